@@ -1,0 +1,199 @@
+/*
+ * pyc_b200.h -- C-ABI of the B200-native execution backend for PyC's
+ * compiler-next runtime (libpyc_b200.so).
+ *
+ * Part 1 declares the eight symbols that PyC's own GPU half exports
+ * (src/compiler/runtime/cuda_backend.c + src/compiler/cutlass_kernels/) with
+ * identical names, argument meaning and return conventions, so that PyC's
+ * compiler_api.c, its Rust FFI (src/runtime/vortex_core/src/ffi/mod.rs:161-186)
+ * and its Python ctypes layer (python/pyc/compiler/__init__.py:187-190) bind to
+ * this library without change.
+ *
+ * Part 2 is additive: entry points for work PyC's IR cannot express (batched
+ * attention, conv2d with a bias/ReLU epilogue, fp8-weight FFN block) and for
+ * GPU-aware callers (caller-owned stream, measured autotune).  Nothing in part
+ * 2 changes the meaning of part 1.
+ *
+ * All pointers named "device" must be CUDA device (or managed) addresses on the
+ * current device.  All functions are thread-safe per device; work on one device
+ * is serialised behind that device's context lock.
+ */
+#ifndef PYC_B200_H
+#define PYC_B200_H
+
+#include "pyc_b200_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ======================================================================= *
+ * Part 1 -- drop-in symbols                                                *
+ * ======================================================================= */
+
+/* Replaces pyc_cuda_dispatch_trace_init (include/pyc/cuda_backend.h:61,
+ * src/compiler/runtime/cuda_backend.c:235-247): zero the trace, reason = "". */
+void pyc_cuda_dispatch_trace_init(pyc_cuda_dispatch_trace* trace);
+
+/* Replaces pyc_cuda_current_hardware_family (cuda_backend.h:62,
+ * cuda_backend.c:249-301).  The PyC enum has no Blackwell member; as in PyC,
+ * compute capability >= 9 reports PYC_KERNEL_HARDWARE_HOPPER, so a B200 gets
+ * the "hopper" scoring affinity.  PYC_CUDA_FORCE_HARDWARE_FAMILY=
+ * hopper|ada|generic overrides.  No device => GENERIC. */
+pyc_kernel_hardware_family pyc_cuda_current_hardware_family(void);
+
+/* Replaces pyc_cuda_dispatch (cuda_backend.h:87-96, cuda_backend.c:2808-2928):
+ * run one compiled IR module.  inputs[]/outputs[] follow the module's
+ * INPUT/OUTPUT op order.  Each pyc_tensor.data may be a host pointer (staged
+ * through pinned memory, as PyC does) or a device pointer (zero copy).
+ * Supported op kinds: INPUT, MATMUL, ADD (same shape, row bias [N], scalar [1]),
+ * RELU, GELU (erf), REDUCE_SUM (trailing axis), LAYERNORM (last axis, eps 1e-5,
+ * optional gamma/beta as input_ids[1..2]), OUTPUT; dtypes F32, BF16, F16.
+ * The op sequence is fused (matmul+bias+activation), placed in one device
+ * arena by lifetime, captured once as a CUDA graph and replayed afterwards.
+ * Returns OK (ran on the GPU), FALLBACK (cpu_executor ran: no device, an env
+ * switch, or an op kind the GPU path does not know) or ERROR (NULL argument,
+ * PYC_CUDA_FORCE_ERROR, a CUDA failure, or the fallback failed too).
+ * Env switches honoured: PYC_CUDA_DISABLE, PYC_CUDA_FORCE_ERROR,
+ * PYC_CUDA_FORCE_FALLBACK, PYC_CUDA_SIMULATE_AVAILABLE,
+ * PYC_CUDA_ENABLE_GRAPH_REPLAY, PYC_CUDA_ASSUME_STATIC_LHS/RHS,
+ * PYC_CUDA_SKIP_HOST_OUTPUT_COPY.  trace->reason is always NUL-terminated. */
+pyc_cuda_dispatch_status pyc_cuda_dispatch(
+    const pyc_ir_module* module, const pyc_tensor* inputs, size_t input_count,
+    pyc_tensor* outputs, size_t output_count,
+    pyc_cpu_executor_fn cpu_executor, void* executor_ctx, pyc_cuda_dispatch_trace* trace);
+
+/* Replaces pyc_cutlass_gemm_dispatch (cuda_backend.h:105-114,
+ * cutlass_kernels/gemm/kernel.cu:151-203): C[M,N] = alpha*A[M,K]*B + beta*C on
+ * device pointers, row-major, leading dimensions K / N / N, enqueued on
+ * `stream` (cudaStream_t) without synchronising.  `symbol` picks dtype and
+ * tile configuration; PyC's four legacy names are accepted as aliases
+ * (cutlass_gemm_tensorcore_bf16: B row-major [K,N]; cutlass_gemm_tensorcore_f16:
+ * B column-major as in kernel.cu:161-174; cutlass_gemm_simt_f32 and
+ * ada_gemm_k64_warp32_async_f32: fp32).  Returns 0, or -1 for an unknown symbol,
+ * a bad shape or a launch failure. */
+int pyc_cutlass_gemm_dispatch(const char* symbol, int M, int N, int K,
+                              const void* A, const void* B, void* C,
+                              float alpha, float beta, void* stream);
+
+/* Replaces pyc_cutlass_conv2d_dispatch (cuda_backend.h:116-126,
+ * cutlass_kernels/conv2d/kernel.cu:80-111): NHWC forward convolution, filter
+ * KRSC, cross-correlation, dilation 1, groups 1, output [N,P,Q,K] with
+ * P=(H-R+2*pad_h)/stride_h+1.  Symbols: b200_conv2d_fprop_bf16 /
+ * b200_conv2d_fprop_f16 and PyC's cutlass_conv2d_fprop_{f16,bf16}. */
+int pyc_cutlass_conv2d_dispatch(const char* symbol, int N, int H, int W, int C_in,
+                                int K, int R, int S, int pad_h, int pad_w,
+                                int stride_h, int stride_w,
+                                const void* input, const void* filter, void* output, void* stream);
+
+/* Replaces pyc_cutlass_attention_dispatch (cuda_backend.h:128-138,
+ * cutlass_kernels/attention/kernel.cu:95-122): one head,
+ * Out[seq_len,d_head] = softmax(scale * Q K^T) V, as the header comment at
+ * attention/kernel.cu:6-8 defines it (PyC's own kernel body is an identity
+ * copy).  Symbols: b200_attention_bf16, b200_attention_bf16_causal,
+ * b200_attention_f16[_causal], and PyC's cutlass_attention_{f16,bf16}
+ * (non-causal). */
+int pyc_cutlass_attention_dispatch(const char* symbol, int seq_len, int d_head,
+                                   const void* Q, const void* K, const void* V, void* Out,
+                                   float scale, void* stream);
+
+/* Replaces pyc_cutlass_kernel_count (cuda_backend.h:143, registry/init.cu:88-91):
+ * number of CUDA kernels registered under op_key ("matmul", "conv2d",
+ * "attention"). */
+int pyc_cutlass_kernel_count(const char* op_key);
+
+/* Replaces pyc_cutlass_registry_init (registry/init.cu:32-78): register every
+ * kernel of this library in PyC's kernel registry (when PyC's
+ * kernel_registry.c is linked in the same process) and in the library's own
+ * symbol table; honours PYC_PROMOTED_GEMM_SYMBOL.  Idempotent. */
+void pyc_cutlass_registry_init(void);
+
+/* ======================================================================= *
+ * Part 2 -- additive entry points (no counterpart in PyC)                  *
+ * ======================================================================= */
+
+typedef enum { PYC_B200_ACT_NONE = 0, PYC_B200_ACT_RELU = 1, PYC_B200_ACT_GELU = 2 } pyc_b200_activation;
+typedef enum { PYC_B200_ADD_NONE = 0, PYC_B200_ADD_MATRIX = 1, PYC_B200_ADD_ROW_BIAS = 2, PYC_B200_ADD_SCALAR = 3 } pyc_b200_add_mode;
+
+/* Fused GEMM: D = act(alpha * A*B + add), device pointers, row-major.
+ * dtype is the storage type of A, B, add and D (F32, BF16 or F16); the
+ * accumulator is fp32.  b_col_major != 0 means B is stored [N,K].
+ * symbol may be NULL (the registry's current choice for dtype/shape). */
+typedef struct {
+    const char* symbol;
+    pyc_dtype dtype;
+    int M, N, K;
+    const void* A;
+    const void* B;
+    void* D;
+    int b_col_major;
+    float alpha;
+    pyc_b200_add_mode add_mode;
+    const void* add;              /* [M,N], [N] or [1] of dtype */
+    pyc_b200_activation act;
+} pyc_b200_gemm_args;
+int pyc_b200_gemm(const pyc_b200_gemm_args* args, void* stream);
+
+/* Elementwise / reduction ops on device pointers (HBM-bound kernels). */
+int pyc_b200_add(pyc_dtype dtype, const void* a, const void* b, void* out, size_t elems, void* stream);
+int pyc_b200_bias_act(pyc_dtype dtype, const void* x, const void* add, pyc_b200_add_mode add_mode,
+                      pyc_b200_activation act, void* out, size_t rows, size_t cols, void* stream);
+int pyc_b200_layernorm(pyc_dtype dtype, const void* x, const void* gamma, const void* beta,
+                       void* out, size_t rows, size_t cols, float eps, void* stream);
+int pyc_b200_softmax(pyc_dtype dtype, const void* x, void* out, size_t rows, size_t cols, void* stream);
+int pyc_b200_reduce_sum(pyc_dtype dtype, const void* x, void* out, size_t rows, size_t cols, void* stream);
+
+/* Batched attention: Q,K,V,Out are [batch_heads, seq_len, d_head] contiguous. */
+int pyc_b200_attention(pyc_dtype dtype, int batch_heads, int seq_len, int d_head,
+                       const void* Q, const void* K, const void* V, void* Out,
+                       float scale, int causal, void* stream);
+
+/* conv2d forward with fused bias[K] (may be NULL) and optional ReLU. */
+int pyc_b200_conv2d(pyc_dtype dtype, int N, int H, int W, int C_in, int K, int R, int S,
+                    int pad_h, int pad_w, int stride_h, int stride_w,
+                    const void* input, const void* filter, const void* bias, int relu,
+                    void* output, void* stream);
+
+/* Time every registered tile configuration for (dtype, M, N, K) with CUDA
+ * events, feed the measured milliseconds to PyC's registry
+ * (pyc_kernel_benchmark_update_symbol) when it is linked, remember the winner
+ * for later NULL-symbol calls, and write its name to best_symbol.
+ * Returns the number of configurations timed, or -1. */
+int pyc_b200_autotune_gemm(pyc_dtype dtype, int M, int N, int K, int iters,
+                           char* best_symbol, size_t best_symbol_size, double* best_ms);
+
+/* Device arena / graph cache telemetry for the last pyc_cuda_dispatch on the
+ * current device. */
+typedef struct {
+    size_t arena_bytes;           /* size of the device arena */
+    size_t plan_peak_bytes;       /* peak of the lifetime plan */
+    size_t plan_total_bytes;      /* sum of all intermediate tensors */
+    size_t graphs_cached;
+    size_t graph_replays;
+    size_t kernels_per_graph;
+    size_t kernel_launches_total; /* kernels this library has launched so far */
+} pyc_b200_runtime_info;
+int pyc_b200_get_runtime_info(pyc_b200_runtime_info* out);
+
+/* GPU-aware callers: make pyc_cuda_dispatch enqueue on `stream` and, when
+ * async != 0 and every tensor is a device pointer, return without
+ * synchronising.  Pass NULL/0 to restore the default (private stream, sync). */
+int pyc_b200_set_stream(void* stream, int async);
+
+/* Kernels never spin without a limit: a wait that runs out writes a code to a
+ * per-device status word and the kernel returns.  This reads that word
+ * (synchronising the library's stream): 0 = fine, otherwise
+ * (site << 8) | 1, or -1 if no device. */
+int pyc_b200_device_status(void);
+
+/* Last error text of the calling thread ("" when none). */
+const char* pyc_b200_last_error(void);
+
+/* Free every device allocation, graph and stream the library owns on the
+ * current device. */
+void pyc_b200_shutdown(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PYC_B200_H */

@@ -1,0 +1,181 @@
+"""ctypes binding of libpyc_b200.so: the calls a PyC host makes at the backend seam.
+
+`dispatch()` is pyc_cuda_dispatch (include/pyc/cuda_backend.h:87-96 in PyC);
+`gemm_by_symbol()` is pyc_cutlass_gemm_dispatch (cuda_backend.h:105-114); the
+rest are the additive pyc_b200_* entry points.  There is no CPU path here: if
+the library is missing, or a call does not run on the GPU, these raise.
+"""
+import ctypes as C
+import os
+
+from . import abi
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libpyc_b200.so")
+
+EXPORTS = [
+    # drop-in symbols (PyC names)
+    "pyc_cuda_dispatch_trace_init", "pyc_cuda_current_hardware_family", "pyc_cuda_dispatch",
+    "pyc_cutlass_gemm_dispatch", "pyc_cutlass_conv2d_dispatch", "pyc_cutlass_attention_dispatch",
+    "pyc_cutlass_kernel_count", "pyc_cutlass_registry_init",
+    # additive
+    "pyc_b200_gemm", "pyc_b200_add", "pyc_b200_bias_act", "pyc_b200_layernorm", "pyc_b200_softmax",
+    "pyc_b200_reduce_sum", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm",
+    "pyc_b200_get_runtime_info", "pyc_b200_set_stream", "pyc_b200_device_status", "pyc_b200_last_error",
+    "pyc_b200_shutdown",
+]
+
+_lib = None
+
+
+class BackendError(RuntimeError):
+    pass
+
+
+def load():
+    """Load the CUDA library; fail loudly when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise BackendError(f"{LIB_PATH} is missing: run `python -m pyc_b200.build` (needs nvcc); there is no CPU fallback")
+    L = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+    vp, i, sz, f = C.c_void_p, C.c_int, C.c_size_t, C.c_float
+    L.pyc_cuda_dispatch_trace_init.argtypes = [C.POINTER(abi.DispatchTrace)]
+    L.pyc_cuda_dispatch_trace_init.restype = None
+    L.pyc_cuda_current_hardware_family.restype = i
+    L.pyc_cuda_dispatch.argtypes = [C.POINTER(abi.IrModule), C.POINTER(abi.Tensor), sz, C.POINTER(abi.Tensor), sz,
+                                    abi.CPU_EXECUTOR_FN, vp, C.POINTER(abi.DispatchTrace)]
+    L.pyc_cuda_dispatch.restype = i
+    L.pyc_cutlass_gemm_dispatch.argtypes = [C.c_char_p, i, i, i, vp, vp, vp, f, f, vp]
+    L.pyc_cutlass_conv2d_dispatch.argtypes = [C.c_char_p] + [i] * 11 + [vp, vp, vp, vp]
+    L.pyc_cutlass_attention_dispatch.argtypes = [C.c_char_p, i, i, vp, vp, vp, vp, f, vp]
+    L.pyc_cutlass_kernel_count.argtypes = [C.c_char_p]
+    L.pyc_cutlass_registry_init.restype = None
+    L.pyc_b200_gemm.argtypes = [C.POINTER(abi.GemmArgs), vp]
+    L.pyc_b200_add.argtypes = [i, vp, vp, vp, sz, vp]
+    L.pyc_b200_bias_act.argtypes = [i, vp, vp, i, i, vp, sz, sz, vp]
+    L.pyc_b200_layernorm.argtypes = [i, vp, vp, vp, vp, sz, sz, f, vp]
+    L.pyc_b200_softmax.argtypes = [i, vp, vp, sz, sz, vp]
+    L.pyc_b200_reduce_sum.argtypes = [i, vp, vp, sz, sz, vp]
+    L.pyc_b200_attention.argtypes = [i, i, i, i, vp, vp, vp, vp, f, i, vp]
+    L.pyc_b200_conv2d.argtypes = [i] * 12 + [vp, vp, vp, i, vp, vp]
+    L.pyc_b200_autotune_gemm.argtypes = [i, i, i, i, i, C.c_char_p, sz, C.POINTER(C.c_double)]
+    L.pyc_b200_get_runtime_info.argtypes = [C.POINTER(abi.RuntimeInfo)]
+    L.pyc_b200_set_stream.argtypes = [vp, i]
+    L.pyc_b200_last_error.restype = C.c_char_p
+    L.pyc_b200_shutdown.restype = None
+    _lib = L
+    return L
+
+
+def last_error():
+    return (load().pyc_b200_last_error() or b"").decode()
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise BackendError(f"{what} failed (rc={rc}): {last_error()}")
+
+
+@abi.CPU_EXECUTOR_FN
+def _refuse_cpu(module, inputs, n_in, outputs, n_out, ctx):
+    # The seam requires a cpu_executor argument (PyC rejects NULL); this one
+    # makes any attempt to leave the GPU an error instead of a silent fallback.
+    return -1
+
+
+def make_tensor(ptr, nbytes, dtype, shape):
+    t = abi.Tensor()
+    t.data = ptr
+    t.size_bytes = nbytes
+    t.dtype = dtype
+    t.shape = abi.Shape.of(shape)
+    return t
+
+
+def dispatch(module, inputs, outputs, cpu_executor=None, require_gpu=True):
+    """pyc_cuda_dispatch.  inputs/outputs: lists of abi.Tensor (host or device pointers).
+    Returns (status, trace).  With require_gpu (default) anything but a GPU run raises."""
+    L = load()
+    ins = (abi.Tensor * len(inputs))(*inputs)
+    outs = (abi.Tensor * len(outputs))(*outputs)
+    trace = abi.DispatchTrace()
+    st = L.pyc_cuda_dispatch(C.byref(module), ins, len(inputs), outs, len(outputs),
+                             cpu_executor or _refuse_cpu, None, C.byref(trace))
+    if require_gpu and (st != abi.DISPATCH_OK or trace.fallback_to_cpu or not trace.reason.startswith(b"b200_")):
+        raise BackendError(f"pyc_cuda_dispatch did not run on the GPU: status={st} reason={trace.reason.decode()!r} {last_error()}")
+    return st, trace
+
+
+def gemm_by_symbol(symbol, M, N, K, A, B, Cptr, alpha=1.0, beta=0.0, stream=0):
+    _check(load().pyc_cutlass_gemm_dispatch(symbol.encode(), M, N, K, A, B, Cptr, alpha, beta, stream), f"pyc_cutlass_gemm_dispatch({symbol})")
+
+
+def gemm(dtype, M, N, K, A, B, D, add=None, add_mode=abi.ADD_NONE, act=abi.ACT_NONE, alpha=1.0,
+         b_col_major=False, symbol=None, stream=0):
+    a = abi.GemmArgs()
+    a.symbol = symbol.encode() if symbol else None
+    a.dtype, a.M, a.N, a.K = dtype, M, N, K
+    a.A, a.B, a.D = A, B, D
+    a.b_col_major = int(b_col_major)
+    a.alpha = alpha
+    a.add_mode = add_mode if add else abi.ADD_NONE
+    a.add = add
+    a.act = act
+    _check(load().pyc_b200_gemm(C.byref(a), stream), "pyc_b200_gemm")
+
+
+def add(dtype, a, b, out, elems, stream=0):
+    _check(load().pyc_b200_add(dtype, a, b, out, elems, stream), "pyc_b200_add")
+
+
+def bias_act(dtype, x, addp, add_mode, act, out, rows, cols, stream=0):
+    _check(load().pyc_b200_bias_act(dtype, x, addp, add_mode, act, out, rows, cols, stream), "pyc_b200_bias_act")
+
+
+def layernorm(dtype, x, gamma, beta, out, rows, cols, eps=1e-5, stream=0):
+    _check(load().pyc_b200_layernorm(dtype, x, gamma, beta, out, rows, cols, eps, stream), "pyc_b200_layernorm")
+
+
+def softmax(dtype, x, out, rows, cols, stream=0):
+    _check(load().pyc_b200_softmax(dtype, x, out, rows, cols, stream), "pyc_b200_softmax")
+
+
+def reduce_sum(dtype, x, out, rows, cols, stream=0):
+    _check(load().pyc_b200_reduce_sum(dtype, x, out, rows, cols, stream), "pyc_b200_reduce_sum")
+
+
+def attention(dtype, batch_heads, seq, d, q, k, v, out, scale, causal, stream=0):
+    _check(load().pyc_b200_attention(dtype, batch_heads, seq, d, q, k, v, out, scale, int(causal), stream), "pyc_b200_attention")
+
+
+def conv2d(dtype, N, H, W, Cin, K, R, S, pad, stride, x, w, bias, relu, out, stream=0):
+    _check(load().pyc_b200_conv2d(dtype, N, H, W, Cin, K, R, S, pad[0], pad[1], stride[0], stride[1], x, w, bias, int(relu), out, stream), "pyc_b200_conv2d")
+
+
+def autotune_gemm(dtype, M, N, K, iters=5):
+    buf = C.create_string_buffer(abi.PYC_KERNEL_SYMBOL_MAX)
+    ms = C.c_double()
+    n = load().pyc_b200_autotune_gemm(dtype, M, N, K, iters, buf, len(buf), C.byref(ms))
+    if n < 0:
+        raise BackendError(f"pyc_b200_autotune_gemm failed: {last_error()}")
+    return buf.value.decode(), ms.value, n
+
+
+def runtime_info():
+    info = abi.RuntimeInfo()
+    load().pyc_b200_get_runtime_info(C.byref(info))
+    return info
+
+
+def kernel_count(op_key):
+    return load().pyc_cutlass_kernel_count(op_key.encode())
+
+
+def set_stream(stream, async_=False):
+    _check(load().pyc_b200_set_stream(stream, int(async_)), "pyc_b200_set_stream")
+
+
+def device_status():
+    return load().pyc_b200_device_status()

@@ -1,0 +1,352 @@
+// HBM-bound elementwise and row-reduction kernels: add, bias+activation,
+// layernorm, softmax, reduce_sum.  128-bit coalesced loads/stores, warp-shuffle
+// reductions, each row read from HBM exactly once (kept in registers between the
+// statistics pass and the normalisation pass).
+//
+// These are the ops PyC's IR names (include/pyc/ir.h:29-39) but its executors do
+// not implement on the GPU: ADD/RELU run as host loops after the GEMM
+// (src/compiler/runtime/cuda_backend.c:1697-1742), GELU / LAYERNORM / REDUCE_SUM
+// are rejected (cuda_backend.c:1153-1159).  Semantics: GELU = exact erf form;
+// LAYERNORM = last axis, biased variance, eps inside the square root, optional
+// gamma/beta; REDUCE_SUM / softmax = over the trailing axis.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "internal.h"
+
+namespace b200 {
+namespace {
+
+template <typename T> struct VecInfo;
+template <> struct VecInfo<float> { static constexpr int N = 4; };
+template <> struct VecInfo<__nv_bfloat16> { static constexpr int N = 8; };
+template <> struct VecInfo<__half> { static constexpr int N = 8; };
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+__device__ __forceinline__ void from_f(float& d, float v) { d = v; }
+__device__ __forceinline__ void from_f(__nv_bfloat16& d, float v) { d = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void from_f(__half& d, float v) { d = __float2half_rn(v); }
+
+// VEC elements of T as one 16-byte (or, for VEC == 1, scalar) access.
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec(const T* p, float (&f)[VEC]) {
+    if constexpr (VEC == 1) {
+        f[0] = to_f(*p);
+    } else {
+        union { uint4 u; T t[VEC]; } x;
+        x.u = __ldg(reinterpret_cast<const uint4*>(p));
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) f[i] = to_f(x.t[i]);
+    }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_vec(T* p, const float (&f)[VEC]) {
+    if constexpr (VEC == 1) {
+        from_f(*p, f[0]);
+    } else {
+        union { uint4 u; T t[VEC]; } x;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) from_f(x.t[i], f[i]);
+        *reinterpret_cast<uint4*>(p) = x.u;
+    }
+}
+
+__device__ __forceinline__ float act_fn(float v, int act) {
+    if (act == PYC_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
+    if (act == PYC_B200_ACT_GELU) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    return v;
+}
+
+// ------------------------------------------------------------------ add ------
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t nvec) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float x[VEC], y[VEC];
+        load_vec<T, VEC>(a + i * VEC, x);
+        load_vec<T, VEC>(b + i * VEC, y);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) x[j] += y[j];
+        store_vec<T, VEC>(out + i * VEC, x);
+    }
+}
+
+// --------------------------------------------------------- bias + activation --
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, const T* __restrict__ add, int add_mode, int act,
+                                                      T* __restrict__ out, size_t nvec, size_t cols) {
+    const float sadd = add_mode == PYC_B200_ADD_SCALAR ? to_f(add[0]) : 0.0f;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float v[VEC];
+        load_vec<T, VEC>(x + i * VEC, v);
+        if (add_mode == PYC_B200_ADD_MATRIX || add_mode == PYC_B200_ADD_ROW_BIAS) {
+            float y[VEC];
+            const size_t off = add_mode == PYC_B200_ADD_MATRIX ? i * VEC : (i * VEC) % cols;
+            load_vec<T, VEC>(add + off, y);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[j] += y[j];
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) v[j] = act_fn(v[j] + sadd, act);
+        store_vec<T, VEC>(out + i * VEC, v);
+    }
+}
+
+// ------------------------------------------------------------ row reductions --
+enum RowOp { ROW_LAYERNORM = 0, ROW_SOFTMAX = 1, ROW_SUM = 2 };
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if constexpr (THREADS > 32) {
+        const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+        __syncthreads();
+        if (l == 0) scratch[w] = v;
+        __syncthreads();
+        v = l < THREADS / 32 ? scratch[l] : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    }
+    return v;
+}
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if constexpr (THREADS > 32) {
+        const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+        __syncthreads();
+        if (l == 0) scratch[w] = v;
+        __syncthreads();
+        v = l < THREADS / 32 ? scratch[l] : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    }
+    return v;
+}
+
+// One row per group of THREADS threads (THREADS = 32: several rows per CTA).
+// Each thread owns up to VPT vectors of its row in registers; CACHED == false is
+// the any-width form that re-reads the row from global memory instead.
+template <typename T, int VEC, int THREADS, int VPT, bool CACHED, int OP>
+__global__ void __launch_bounds__(THREADS >= 128 ? THREADS : 128)
+row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
+           size_t rows, size_t cols, float eps) {
+    constexpr int ROWS_PER_CTA = THREADS >= 128 ? 1 : 128 / THREADS;
+    __shared__ float scratch[8];
+    const int tid = THREADS >= 128 ? threadIdx.x : (threadIdx.x % THREADS);
+    const size_t nvec = cols / VEC;
+    for (size_t row = blockIdx.x * static_cast<size_t>(ROWS_PER_CTA) + (THREADS >= 128 ? 0 : threadIdx.x / THREADS);
+         row < rows; row += static_cast<size_t>(gridDim.x) * ROWS_PER_CTA) {
+        const T* xr = x + row * cols;
+        T* orow = out + (OP == ROW_SUM ? 0 : row * cols);
+        float v[CACHED ? VPT : 1][VEC];
+        float s = 0.0f, mx = -INFINITY;
+        if constexpr (CACHED) {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const size_t vi = tid + static_cast<size_t>(i) * THREADS;
+                if (vi < nvec) {
+                    load_vec<T, VEC>(xr + vi * VEC, v[i]);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) { s += v[i][j]; mx = fmaxf(mx, v[i][j]); }
+                }
+            }
+        } else {
+            for (size_t vi = tid; vi < nvec; vi += THREADS) {
+                load_vec<T, VEC>(xr + vi * VEC, v[0]);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) { s += v[0][j]; mx = fmaxf(mx, v[0][j]); }
+            }
+        }
+        if constexpr (OP == ROW_SUM) {
+            s = block_sum<THREADS>(s, scratch);
+            if (tid == 0) from_f(out[row], s);
+        } else if constexpr (OP == ROW_LAYERNORM) {
+            const float mean = block_sum<THREADS>(s, scratch) / static_cast<float>(cols);
+            float ss = 0.0f;
+            if constexpr (CACHED) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+                    if (tid + static_cast<size_t>(i) * THREADS < nvec)
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) { const float d = v[i][j] - mean; ss += d * d; }
+            } else {
+                for (size_t vi = tid; vi < nvec; vi += THREADS) {
+                    load_vec<T, VEC>(xr + vi * VEC, v[0]);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) { const float d = v[0][j] - mean; ss += d * d; }
+                }
+            }
+            const float rstd = rsqrtf(block_sum<THREADS>(ss, scratch) / static_cast<float>(cols) + eps);
+            auto finish = [&](float (&val)[VEC], size_t vi) {
+                float g[VEC], b[VEC];
+                if (gamma) load_vec<T, VEC>(gamma + vi * VEC, g);
+                if (beta) load_vec<T, VEC>(beta + vi * VEC, b);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) {
+                    float y = (val[j] - mean) * rstd;
+                    if (gamma) y *= g[j];
+                    if (beta) y += b[j];
+                    val[j] = y;
+                }
+                store_vec<T, VEC>(orow + vi * VEC, val);
+            };
+            if constexpr (CACHED) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) { const size_t vi = tid + static_cast<size_t>(i) * THREADS; if (vi < nvec) finish(v[i], vi); }
+            } else {
+                for (size_t vi = tid; vi < nvec; vi += THREADS) { load_vec<T, VEC>(xr + vi * VEC, v[0]); finish(v[0], vi); }
+            }
+        } else {  // softmax
+            mx = block_max<THREADS>(mx, scratch);
+            float den = 0.0f;
+            if constexpr (CACHED) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+                    if (tid + static_cast<size_t>(i) * THREADS < nvec)
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) { v[i][j] = __expf(v[i][j] - mx); den += v[i][j]; }
+            } else {
+                for (size_t vi = tid; vi < nvec; vi += THREADS) {
+                    load_vec<T, VEC>(xr + vi * VEC, v[0]);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) den += __expf(v[0][j] - mx);
+                }
+            }
+            const float inv = 1.0f / block_sum<THREADS>(den, scratch);
+            if constexpr (CACHED) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const size_t vi = tid + static_cast<size_t>(i) * THREADS;
+                    if (vi < nvec) {
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) v[i][j] *= inv;
+                        store_vec<T, VEC>(orow + vi * VEC, v[i]);
+                    }
+                }
+            } else {
+                for (size_t vi = tid; vi < nvec; vi += THREADS) {
+                    load_vec<T, VEC>(xr + vi * VEC, v[0]);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) v[0][j] = __expf(v[0][j] - mx) * inv;
+                    store_vec<T, VEC>(orow + vi * VEC, v[0]);
+                }
+            }
+        }
+    }
+}
+
+inline int flat_grid(size_t work_items, int threads) {
+    const size_t blocks = (work_items + threads - 1) / threads;
+    const size_t cap = static_cast<size_t>(sm_count()) * 16;  // 16 resident CTAs of 256 threads would oversubscribe: 8 fit
+    return static_cast<int>(blocks < cap ? (blocks ? blocks : 1) : cap);
+}
+
+inline bool aligned16(const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+template <typename T, int VEC, int OP>
+int launch_row_vec(const T* x, const T* g, const T* b, T* out, size_t rows, size_t cols, float eps, cudaStream_t s) {
+    const size_t nvec = cols / VEC;
+    const size_t max_grid = static_cast<size_t>(sm_count()) * 32;
+#define B200_ROW(THREADS, VPT, CACHED)                                                                        \
+    do {                                                                                                       \
+        constexpr int RPC = (THREADS) >= 128 ? 1 : 128 / (THREADS);                                            \
+        size_t grid = (rows + RPC - 1) / RPC;                                                                  \
+        if (grid > max_grid) grid = max_grid;                                                                  \
+        row_kernel<T, VEC, THREADS, VPT, CACHED, OP><<<static_cast<unsigned>(grid), (THREADS) >= 128 ? (THREADS) : 128, 0, s>>>( \
+            x, g, b, out, rows, cols, eps);                                                                    \
+    } while (0)
+    if (nvec <= 32 * 4) B200_ROW(32, 4, true);
+    else if (nvec <= 128 * 4) B200_ROW(128, 4, true);
+    else if (nvec <= 256 * 4) B200_ROW(256, 4, true);
+    else if (nvec <= 256 * 8) B200_ROW(256, 8, true);
+    else B200_ROW(256, 1, false);
+#undef B200_ROW
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+template <typename T, int OP>
+int launch_row_typed(const void* x, const void* g, const void* b, void* out, size_t rows, size_t cols, float eps, cudaStream_t s) {
+    constexpr int V = VecInfo<T>::N;
+    const bool vec = cols % V == 0 && aligned16(x) && aligned16(g) && aligned16(b) && (OP == ROW_SUM || aligned16(out));
+    if (vec) return launch_row_vec<T, V, OP>(static_cast<const T*>(x), static_cast<const T*>(g), static_cast<const T*>(b), static_cast<T*>(out), rows, cols, eps, s);
+    return launch_row_vec<T, 1, OP>(static_cast<const T*>(x), static_cast<const T*>(g), static_cast<const T*>(b), static_cast<T*>(out), rows, cols, eps, s);
+}
+
+template <int OP>
+int launch_row(pyc_dtype dt, const void* x, const void* g, const void* b, void* out, size_t rows, size_t cols, float eps, cudaStream_t s) {
+    if (rows == 0 || cols == 0) { set_error("row op: empty shape"); return -1; }
+    switch (dt) {
+        case PYC_DTYPE_F32: return launch_row_typed<float, OP>(x, g, b, out, rows, cols, eps, s);
+        case PYC_DTYPE_BF16: return launch_row_typed<__nv_bfloat16, OP>(x, g, b, out, rows, cols, eps, s);
+        case PYC_DTYPE_F16: return launch_row_typed<__half, OP>(x, g, b, out, rows, cols, eps, s);
+        default: set_error("row op: unsupported dtype %d", static_cast<int>(dt)); return -1;
+    }
+}
+
+template <typename T>
+int launch_add_typed(const void* a, const void* b, void* out, size_t n, cudaStream_t s) {
+    constexpr int V = VecInfo<T>::N;
+    if (n % V == 0 && aligned16(a) && aligned16(b) && aligned16(out)) {
+        add_kernel<T, V><<<flat_grid(n / V, 256), 256, 0, s>>>(static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), n / V);
+    } else {
+        add_kernel<T, 1><<<flat_grid(n, 256), 256, 0, s>>>(static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), n);
+    }
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+template <typename T>
+int launch_bias_act_typed(const void* x, const void* add, int add_mode, int act, void* out, size_t rows, size_t cols, cudaStream_t s) {
+    constexpr int V = VecInfo<T>::N;
+    const size_t n = rows * cols;
+    if (!add) add_mode = PYC_B200_ADD_NONE;
+    if (cols % V == 0 && aligned16(x) && aligned16(out) && (add_mode == PYC_B200_ADD_SCALAR || aligned16(add))) {
+        bias_act_kernel<T, V><<<flat_grid(n / V, 256), 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add), add_mode, act, static_cast<T*>(out), n / V, cols);
+    } else {
+        bias_act_kernel<T, 1><<<flat_grid(n, 256), 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add), add_mode, act, static_cast<T*>(out), n, cols);
+    }
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+}  // namespace
+
+int launch_add(pyc_dtype dt, const void* a, const void* b, void* out, size_t n, cudaStream_t s) {
+    if (n == 0) { set_error("add: empty"); return -1; }
+    switch (dt) {
+        case PYC_DTYPE_F32: return launch_add_typed<float>(a, b, out, n, s);
+        case PYC_DTYPE_BF16: return launch_add_typed<__nv_bfloat16>(a, b, out, n, s);
+        case PYC_DTYPE_F16: return launch_add_typed<__half>(a, b, out, n, s);
+        default: set_error("add: unsupported dtype %d", static_cast<int>(dt)); return -1;
+    }
+}
+
+int launch_bias_act(pyc_dtype dt, const void* x, const void* add, int add_mode, int act, void* out, size_t rows, size_t cols, cudaStream_t s) {
+    if (rows == 0 || cols == 0) { set_error("bias_act: empty"); return -1; }
+    switch (dt) {
+        case PYC_DTYPE_F32: return launch_bias_act_typed<float>(x, add, add_mode, act, out, rows, cols, s);
+        case PYC_DTYPE_BF16: return launch_bias_act_typed<__nv_bfloat16>(x, add, add_mode, act, out, rows, cols, s);
+        case PYC_DTYPE_F16: return launch_bias_act_typed<__half>(x, add, add_mode, act, out, rows, cols, s);
+        default: set_error("bias_act: unsupported dtype %d", static_cast<int>(dt)); return -1;
+    }
+}
+
+int launch_layernorm(pyc_dtype dt, const void* x, const void* gamma, const void* beta, void* out, size_t rows, size_t cols, float eps, cudaStream_t s) {
+    return launch_row<ROW_LAYERNORM>(dt, x, gamma, beta, out, rows, cols, eps, s);
+}
+int launch_softmax(pyc_dtype dt, const void* x, void* out, size_t rows, size_t cols, cudaStream_t s) {
+    return launch_row<ROW_SOFTMAX>(dt, x, nullptr, nullptr, out, rows, cols, 0.0f, s);
+}
+int launch_reduce_sum(pyc_dtype dt, const void* x, void* out, size_t rows, size_t cols, cudaStream_t s) {
+    return launch_row<ROW_SUM>(dt, x, nullptr, nullptr, out, rows, cols, 0.0f, s);
+}
+
+}  // namespace b200

@@ -1,0 +1,171 @@
+// fp32-accurate GEMM on the CUDA cores with the same fused epilogue as the
+// tensor-core kernel: D = act(alpha * A*B + add_scale * add).
+//
+// Replaces the fp32 lane of PyC's CUDA backend (cublasGemmEx / cublasLt with
+// TF32 at src/compiler/runtime/cuda_backend.c:770-1081, the CUTLASS SIMT kernel
+// at cutlass_kernels/gemm/kernel.cu:89-99 and the hand-written cp.async kernel
+// at cutlass_kernels/gemm/ada_async_kernel.cu:150-250).  Products are formed
+// from unrounded fp32 inputs and accumulated with FMA in ascending k, so results
+// stay within 1e-5 (norm-wise) of PyC's CPU executor; TF32 would not.
+// It is also the any-shape path for bf16/f16 matrices whose leading dimensions
+// do not satisfy TMA's 16-byte stride rule.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "internal.h"
+
+namespace b200 {
+namespace {
+
+constexpr int BK = 16;
+
+__device__ __forceinline__ float ldf(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float ldf(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void stf(__half* p, float v) { *p = __float2half_rn(v); }
+
+__device__ __forceinline__ float act_fn(float v, int act) {
+    if (act == PYC_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
+    if (act == PYC_B200_ACT_GELU) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    return v;
+}
+
+struct SimtParams {
+    const void* A; const void* B; void* D; const void* add;
+    int M, N, K;
+    int b_col_major, add_mode, act;
+    float alpha, add_scale;
+};
+
+template <typename T, int BM, int BN, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_simt_kernel(SimtParams p) {
+    constexpr int THREADS = (BM / TM) * (BN / TN);
+    constexpr int A_PER = BM * BK / THREADS;
+    constexpr int B_PER = BK * BN / THREADS;
+    static_assert(BM * BK % THREADS == 0 && BK * BN % THREADS == 0, "tile/threads mismatch");
+    __shared__ float As[2][BK][BM + 4];
+    __shared__ float Bs[2][BK][BN + 4];
+
+    const T* A = reinterpret_cast<const T*>(p.A);
+    const T* B = reinterpret_cast<const T*>(p.B);
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int M = p.M, N = p.N, K = p.K;
+
+    float ra[A_PER], rb[B_PER];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < A_PER; ++i) {  // A tile: consecutive threads walk k (contiguous in memory)
+            const int e = tid + i * THREADS, r = e / BK, c = e % BK;
+            const int gr = m0 + r, gc = k0 + c;
+            ra[i] = (gr < M && gc < K) ? ldf(A + static_cast<size_t>(gr) * K + gc) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < B_PER; ++i) {
+            const int e = tid + i * THREADS;
+            if (p.b_col_major) {  // B stored [N,K]: walk k fastest
+                const int c = e / BK, r = e % BK, gr = k0 + r, gc = n0 + c;
+                rb[i] = (gr < K && gc < N) ? ldf(B + static_cast<size_t>(gc) * K + gr) : 0.0f;
+            } else {
+                const int r = e / BN, c = e % BN, gr = k0 + r, gc = n0 + c;
+                rb[i] = (gr < K && gc < N) ? ldf(B + static_cast<size_t>(gr) * N + gc) : 0.0f;
+            }
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < A_PER; ++i) { const int e = tid + i * THREADS; As[buf][e % BK][e / BK] = ra[i]; }
+#pragma unroll
+        for (int i = 0; i < B_PER; ++i) {
+            const int e = tid + i * THREADS;
+            if (p.b_col_major) Bs[buf][e % BK][e / BK] = rb[i]; else Bs[buf][e / BN][e % BN] = rb[i];
+        }
+    };
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        const bool more = k0 + BK < K;
+        if (more) fetch(k0 + BK);
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[buf][kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) b[j] = Bs[buf][kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (more) { stash(buf ^ 1); __syncthreads(); buf ^= 1; }
+    }
+
+    T* D = reinterpret_cast<T*>(p.D);
+    const T* add = reinterpret_cast<const T*>(p.add);
+    const float sadd = p.add_mode == PYC_B200_ADD_SCALAR ? p.add_scale * ldf(add) : 0.0f;
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = m0 + ty * TM + i;
+        if (r >= M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int c = n0 + tx * TN + j;
+            if (c >= N) continue;
+            float v = p.alpha * acc[i][j] + sadd;
+            if (p.add_mode == PYC_B200_ADD_ROW_BIAS) v += p.add_scale * ldf(add + c);
+            else if (p.add_mode == PYC_B200_ADD_MATRIX) v += p.add_scale * ldf(add + static_cast<size_t>(r) * N + c);
+            stf(D + static_cast<size_t>(r) * N + c, act_fn(v, p.act));
+        }
+    }
+}
+
+template <typename T, int BM, int BN, int TM, int TN>
+int launch_one(const SimtParams& sp, cudaStream_t stream) {
+    dim3 grid((sp.N + BN - 1) / BN, (sp.M + BM - 1) / BM);
+    gemm_simt_kernel<T, BM, BN, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, stream>>>(sp);
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+template <typename T>
+int launch_typed(const GemmConfig& cfg, const SimtParams& sp, cudaStream_t stream) {
+    if (cfg.bm == 128 && cfg.bn == 128) return launch_one<T, 128, 128, 8, 8>(sp, stream);
+    if (cfg.bm == 64 && cfg.bn == 64) return launch_one<T, 64, 64, 4, 4>(sp, stream);
+    if (cfg.bm == 32 && cfg.bn == 64) return launch_one<T, 32, 64, 2, 4>(sp, stream);
+    set_error("no SIMT GEMM instance for tile %dx%d", cfg.bm, cfg.bn);
+    return -1;
+}
+
+}  // namespace
+
+int launch_gemm_simt(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream) {
+    SimtParams sp;
+    sp.A = p.A; sp.B = p.B; sp.D = p.D; sp.add = p.add;
+    sp.M = p.M; sp.N = p.N; sp.K = p.K;
+    sp.b_col_major = p.b_col_major ? 1 : 0;
+    sp.add_mode = p.add ? p.add_mode : PYC_B200_ADD_NONE;
+    sp.act = p.act; sp.alpha = p.alpha; sp.add_scale = p.add_scale;
+    switch (p.dtype) {
+        case PYC_DTYPE_F32: return launch_typed<float>(cfg, sp, stream);
+        case PYC_DTYPE_BF16: return launch_typed<__nv_bfloat16>(cfg, sp, stream);
+        case PYC_DTYPE_F16: return launch_typed<__half>(cfg, sp, stream);
+        default: set_error("SIMT GEMM: unsupported dtype %d", static_cast<int>(p.dtype)); return -1;
+    }
+}
+
+}  // namespace b200

@@ -1,0 +1,325 @@
+// bf16 / f16 GEMM on the 5th-generation tensor cores (tcgen05) with a fused
+// epilogue: D = act(alpha * A*B + add_scale * add).
+//
+// Replaces the tensor-core lane of PyC's CUDA backend: the CUTLASS sm80
+// mma.sync kernels of src/compiler/cutlass_kernels/gemm/kernel.cu:48-84 and the
+// cublasGemmEx bf16/f16 path of src/compiler/runtime/cuda_backend.c:849-896,
+// plus the host-side add/relu loops of cuda_backend.c:1697-1742, which here run
+// in the kernel's epilogue.
+//
+// One persistent CTA per SM, 192 threads, warp-specialised:
+//   warp 0      TMA producer: A [128 x 64] and B [64 x BN] tiles, 128-byte
+//               swizzled, STAGES-deep ring, per-CTA loads only
+//   warp 1      allocates TMEM, one lane issues tcgen05.mma (128 x BN x 16)
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns, bias / activation,
+//               convert, 16-byte global stores
+// Two fp32 accumulators of 128 x BN live in TMEM (2*BN columns), so the
+// epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Data layout: A row-major [M,K] (K-major operand).  B row-major [K,N] is an
+// MN-major operand: each TMA box is 64 n-values (128 B) by 64 k-rows, boxes for
+// consecutive 64-column chunks sit 8 KB apart (descriptor LBO), 8-row groups
+// 1 KB apart (SBO).  B stored [N,K] is the K-major form.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "internal.h"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int GROUP_M = 16;
+
+struct Epilogue {
+    void* D;
+    const void* add;
+    float alpha, add_scale;
+    int add_mode, act, vec_ok;
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == PYC_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
+    if (act == PYC_B200_ACT_GELU) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    return v;
+}
+
+template <int FMT> struct Elem;
+template <> struct Elem<1> {
+    using T = __nv_bfloat16;
+    static __device__ __forceinline__ float to_f(T v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ T from_f(float v) { return __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&p);
+    }
+    static __device__ __forceinline__ void unpack(uint32_t u, float& a, float& b) {
+        a = __uint_as_float(u << 16); b = __uint_as_float(u & 0xffff0000u);
+    }
+};
+template <> struct Elem<0> {
+    using T = __half;
+    static __device__ __forceinline__ float to_f(T v) { return __half2float(v); }
+    static __device__ __forceinline__ T from_f(float v) { return __float2half_rn(v); }
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        __half2 p = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&p);
+    }
+    static __device__ __forceinline__ void unpack(uint32_t u, float& a, float& b) {
+        __half2 p = *reinterpret_cast<__half2*>(&u);
+        float2 f = __half22float2(p); a = f.x; b = f.y;
+    }
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int group = GROUP_M * tiles_n;
+    const int g = tile / group;
+    const int first = g * GROUP_M;
+    const int gm = min(GROUP_M, tiles_m - first);
+    const int local = tile - g * group;
+    tm = first + local % gm;
+    tn = local / gm;
+}
+
+template <int BN, int STAGES, bool B_KMAJOR, int FMT>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               Epilogue ep, int M, int N, int K, int* status) {
+    constexpr int B_STAGE_BYTES = BN * BK * 2;
+    constexpr uint32_t STAGE_TX = A_STAGE_BYTES + B_STAGE_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr uint32_t IDESC = make_idesc(FMT, FMT, 0, B_KMAJOR ? 0 : 1, BM, BN);
+    using E = Elem<FMT>;
+    using T = typename E::T;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+    const uint32_t full0 = smem_u32(bars);
+    const uint32_t empty0 = full0 + 8 * STAGES;
+    const uint32_t tfull0 = empty0 + 8 * STAGES;
+    const uint32_t tempty0 = tfull0 + 16;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_m = (M + BM - 1) / BM;
+    const int tiles_n = (N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                const int m0 = tm * BM, n0 = tn * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, status, 1)) { ok = false; break; }
+                    const uint32_t fb = full0 + 8 * stage;
+                    mbar_arrive_expect_tx(fb, STAGE_TX);
+                    tma_load_2d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, fb, kb * BK, m0);
+                    const uint32_t bdst = smem_u32(sB + stage * B_STAGE_BYTES);
+                    if (B_KMAJOR) {
+                        tma_load_2d(bdst, &tmB, fb, kb * BK, n0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(bdst + j * (BK * 128), &tmB, fb, n0 + j * 64, kb * BK);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, status, 2)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8 * stage, phase, status, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES);
+                    const uint32_t b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+                    for (int k4 = 0; k4 < BK / 16; ++k4) {
+                        const uint64_t adesc = make_smem_desc_sw128(a_base + k4 * 32, 16, 1024);
+                        const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_base + k4 * 32, 16, 1024)
+                                                        : make_smem_desc_sw128(b_base + k4 * 2048, BK * 128, 1024);
+                        umma_f16(d_tmem, adesc, bdesc, IDESC, (kb | k4) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(tfull0 + 8 * acc);
+            }
+        }
+    } else {
+        const int wq = warp & 3;  // TMEM lane quarter this warp may read
+        int it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int row = tm * BM + wq * 32 + lane;
+            const int n0 = tn * BN;
+            if (!mbar_wait(tfull0 + 8 * acc, acc_phase, status, 4)) break;
+            tc_fence_after();
+            T* drow = reinterpret_cast<T*>(ep.D) + static_cast<size_t>(row) * N;
+            const T* addp = reinterpret_cast<const T*>(ep.add);
+            float scalar_add = 0.0f;
+            if (ep.add_mode == PYC_B200_ADD_SCALAR) scalar_add = ep.add_scale * E::to_f(addp[0]);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * BN + c * 32, r);
+                tmem_ld_wait();
+                const int col0 = n0 + c * 32;
+                if (col0 >= N) continue;
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = ep.alpha * __uint_as_float(r[j]) + scalar_add;
+                const bool full_chunk = ep.vec_ok && (col0 + 32 <= N);
+                if (ep.add_mode == PYC_B200_ADD_ROW_BIAS || (ep.add_mode == PYC_B200_ADD_MATRIX && row < M)) {
+                    const T* src = ep.add_mode == PYC_B200_ADD_ROW_BIAS ? addp + col0 : addp + static_cast<size_t>(row) * N + col0;
+                    if (full_chunk) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 u = __ldg(reinterpret_cast<const uint4*>(src) + q);
+                            float a, b;
+                            E::unpack(u.x, a, b); v[q * 8 + 0] += ep.add_scale * a; v[q * 8 + 1] += ep.add_scale * b;
+                            E::unpack(u.y, a, b); v[q * 8 + 2] += ep.add_scale * a; v[q * 8 + 3] += ep.add_scale * b;
+                            E::unpack(u.z, a, b); v[q * 8 + 4] += ep.add_scale * a; v[q * 8 + 5] += ep.add_scale * b;
+                            E::unpack(u.w, a, b); v[q * 8 + 6] += ep.add_scale * a; v[q * 8 + 7] += ep.add_scale * b;
+                        }
+                    } else {
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) v[j] += ep.add_scale * E::to_f(src[j]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], ep.act);
+                if (row < M) {
+                    if (full_chunk) {
+                        uint4* dst = reinterpret_cast<uint4*>(drow + col0);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 u;
+                            u.x = E::pack(v[q * 8 + 0], v[q * 8 + 1]);
+                            u.y = E::pack(v[q * 8 + 2], v[q * 8 + 3]);
+                            u.z = E::pack(v[q * 8 + 4], v[q * 8 + 5]);
+                            u.w = E::pack(v[q * 8 + 6], v[q * 8 + 7]);
+                            dst[q] = u;
+                        }
+                    } else {
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) drow[col0 + j] = E::from_f(v[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+        }
+    }
+
+    // Teardown: every role falls through to here, also after a timed-out wait.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*reinterpret_cast<volatile int*>(status) != ST_OK) {
+            // A wait gave up: give copies and MMAs in flight time to land before the CTA's
+            // shared memory and TMEM go away.
+            for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int BN, int STAGES>
+constexpr size_t tc_smem_bytes() {
+    return 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16;
+}
+
+template <int BN, int STAGES, bool B_KMAJOR, int FMT>
+int launch_instance(const GemmProblem& p, cudaStream_t stream, int* status) {
+    auto kernel = gemm_tc_kernel<BN, STAGES, B_KMAJOR, FMT>;
+    constexpr size_t smem = tc_smem_bytes<BN, STAGES>();
+    static bool attr_set[16] = {};
+    int dev = 0;
+    B200_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 16 && !attr_set[dev]) {
+        B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        attr_set[dev] = true;
+    }
+    CUtensorMap tmA, tmB;
+    if (encode_tmap_2d(&tmA, p.A, 2, p.M, p.K, static_cast<uint64_t>(p.K) * 2, BM, BK) != 0) return -1;
+    if (B_KMAJOR) {
+        if (encode_tmap_2d(&tmB, p.B, 2, p.N, p.K, static_cast<uint64_t>(p.K) * 2, BN, BK) != 0) return -1;
+    } else {
+        if (encode_tmap_2d(&tmB, p.B, 2, p.K, p.N, static_cast<uint64_t>(p.N) * 2, BK, 64) != 0) return -1;
+    }
+    Epilogue ep;
+    ep.D = p.D; ep.add = p.add; ep.alpha = p.alpha; ep.add_scale = p.add_scale;
+    ep.add_mode = p.add ? p.add_mode : PYC_B200_ADD_NONE; ep.act = p.act;
+    const bool aligned = (reinterpret_cast<uintptr_t>(p.D) % 16 == 0) && (p.N % 8 == 0) &&
+                         (ep.add_mode == PYC_B200_ADD_NONE || ep.add_mode == PYC_B200_ADD_SCALAR ||
+                          reinterpret_cast<uintptr_t>(p.add) % 16 == 0);
+    ep.vec_ok = aligned ? 1 : 0;
+    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    kernel<<<grid, 192, smem, stream>>>(tmA, tmB, ep, p.M, p.N, p.K, status);
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+template <int BN, int STAGES>
+int launch_by_layout(const GemmProblem& p, cudaStream_t stream, int* status) {
+    const bool bf16 = p.dtype == PYC_DTYPE_BF16;
+    if (p.b_col_major) return bf16 ? launch_instance<BN, STAGES, true, 1>(p, stream, status) : launch_instance<BN, STAGES, true, 0>(p, stream, status);
+    return bf16 ? launch_instance<BN, STAGES, false, 1>(p, stream, status) : launch_instance<BN, STAGES, false, 0>(p, stream, status);
+}
+
+}  // namespace
+
+int launch_gemm_tc(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream, int* status) {
+    if (cfg.bn == 256 && cfg.stages == 4) return launch_by_layout<256, 4>(p, stream, status);
+    if (cfg.bn == 128 && cfg.stages == 6) return launch_by_layout<128, 6>(p, stream, status);
+    if (cfg.bn == 64 && cfg.stages == 8) return launch_by_layout<64, 8>(p, stream, status);
+    set_error("no tensor-core GEMM instance for tile %dx%dx%d stages %d", cfg.bm, cfg.bn, cfg.bk, cfg.stages);
+    return -1;
+}
+
+}  // namespace b200

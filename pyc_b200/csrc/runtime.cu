@@ -1,0 +1,558 @@
+// Per-device runtime state, tensor-map encoding, the kernel registry bridge and
+// the symbol-addressed / extension C entry points.
+//
+// Replaces the process-global workspace of PyC's CUDA backend
+// (src/compiler/runtime/cuda_backend.c:137-180: three device buffers, cuBLAS
+// handles, one stream, one captured graph behind one global mutex) with one
+// context per device, and the registration code of
+// src/compiler/cutlass_kernels/registry/init.cu:32-92.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "internal.h"
+#include "runtime.h"
+
+// PyC's kernel registry (src/compiler/runtime/kernel_registry.c).  Weak: present
+// when this library is loaded next to PyC's front half, absent stand-alone.
+extern "C" {
+int pyc_kernel_register(const pyc_kernel_desc* desc) __attribute__((weak));
+size_t pyc_kernel_collect(const char* op_key, pyc_backend backend, pyc_kernel_desc* out, size_t cap) __attribute__((weak));
+int pyc_kernel_promote_symbol(const char* op_key, pyc_backend backend, const char* symbol) __attribute__((weak));
+int pyc_kernel_promoted_symbol(const char* op_key, pyc_backend backend, char* out, size_t out_size) __attribute__((weak));
+int pyc_kernel_benchmark_update_symbol(const char* op_key, pyc_backend backend, const char* symbol, double ms) __attribute__((weak));
+}
+
+namespace b200 {
+
+// ------------------------------------------------------------------ errors --
+static thread_local char g_err[512] = "";
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+const char* last_error() { return g_err; }
+
+static std::atomic<size_t> g_launches{0};
+void count_launch(size_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+size_t launches_total() { return g_launches.load(std::memory_order_relaxed); }
+
+// ---------------------------------------------------------------- contexts --
+static std::mutex g_ctx_mu;
+static DeviceContext* g_ctx[kMaxDevices] = {};
+
+DeviceContext* current_context() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        cudaGetLastError();
+        set_error("no usable CUDA device");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    if (g_ctx[dev]) return g_ctx[dev];
+    DeviceContext* c = new DeviceContext();
+    c->device = dev;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { cudaGetLastError(); delete c; set_error("cudaGetDeviceProperties failed"); return nullptr; }
+    c->sm_count = prop.multiProcessorCount;
+    c->cc_major = prop.major;
+    c->cc_minor = prop.minor;
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaMalloc(&c->status_dev, 256) != cudaSuccess ||
+        cudaMemset(c->status_dev, 0, 256) != cudaSuccess ||
+        cudaMallocHost(&c->status_host, 256) != cudaSuccess) {
+        set_error("context setup failed: %s", cudaGetErrorString(cudaGetLastError()));
+        delete c;
+        return nullptr;
+    }
+    *c->status_host = 0;
+    g_ctx[dev] = c;
+    return c;
+}
+
+int sm_count() {
+    DeviceContext* c = current_context();
+    return c ? c->sm_count : 148;
+}
+int* device_status_word() {
+    DeviceContext* c = current_context();
+    return c ? c->status_dev : nullptr;
+}
+int read_device_status(cudaStream_t stream) {
+    DeviceContext* c = current_context();
+    if (!c) return -1;
+    if (cudaMemcpyAsync(c->status_host, c->status_dev, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;
+    return *c->status_host;
+}
+
+int DeviceContext::ensure_arena(size_t bytes) {
+    if (bytes <= arena_bytes) return 0;
+    // Grow-only, like PyC's workspace (cuda_backend.c:303-420); cached graphs hold arena addresses.
+    drop_graphs();
+    if (arena) cudaFree(arena);
+    arena = nullptr; arena_bytes = 0;
+    size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    B200_CUDA_OK(cudaMalloc(&arena, want));
+    arena_bytes = want;
+    return 0;
+}
+int DeviceContext::ensure_pinned(size_t bytes) {
+    if (bytes <= pinned_bytes) return 0;
+    drop_graphs();
+    if (pinned) cudaFreeHost(pinned);
+    pinned = nullptr; pinned_bytes = 0;
+    size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    B200_CUDA_OK(cudaMallocHost(&pinned, want));
+    pinned_bytes = want;
+    return 0;
+}
+void DeviceContext::drop_graphs() {
+    for (auto& kv : graphs) {
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    }
+    graphs.clear();
+}
+
+// ------------------------------------------------------------- tensor maps --
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        else
+            cudaGetLastError();
+    });
+    return fn;
+}
+
+int encode_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, const uint64_t* dims,
+                const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return -1; }
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0) { set_error("tensor map: base address not 16-byte aligned"); return -1; }
+    cuuint64_t gdim[5]; cuuint64_t gstr[4]; cuuint32_t bx[5]; cuuint32_t es[5];
+    for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+    for (int i = 0; i + 1 < rank; ++i) {
+        if (strides_bytes[i] % 16 != 0) { set_error("tensor map: stride %llu not a multiple of 16 bytes", (unsigned long long)strides_bytes[i]); return -1; }
+        gstr[i] = strides_bytes[i];
+    }
+    const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+    const CUresult r = fn(out, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r)); return -1; }
+    return 0;
+}
+
+int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                   uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols) {
+    const uint64_t dims[2] = {cols, rows};
+    const uint64_t strides[1] = {row_stride_bytes};
+    const uint32_t box[2] = {box_cols, box_rows};
+    return encode_tmap(out, base, elem_bytes, 2, dims, strides, box, true);
+}
+
+// ---------------------------------------------------------------- registry --
+struct RegEntry {
+    pyc_kernel_desc desc;
+    double best_ms;
+};
+// Function-local statics: registration runs from a load-time constructor, which may
+// come before this file's namespace-scope objects are constructed.
+struct RegState {
+    std::mutex mu;
+    std::vector<RegEntry> entries;
+    std::map<std::string, std::string> promoted;  // op_key -> symbol (stand-alone mode)
+    bool done = false;
+};
+static RegState& reg_state() { static RegState* s = new RegState(); return *s; }
+#define g_reg_mu (reg_state().mu)
+#define g_reg (reg_state().entries)
+#define g_promoted (reg_state().promoted)
+#define g_reg_done (reg_state().done)
+
+static const GemmConfig kGemmConfigs[] = {
+    // symbol suffix           kind       dtypes (bf16|f16 = 8|4, f32 = 2)  bm   bn   bk  st  prio  smem    workload
+    {"tc_128x256x64_s4", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 256, 64, 4, 100, 197744, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
+    {"tc_128x128x64_s6", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 128, 64, 6, 90, 197776, PYC_KERNEL_WORKLOAD_SQUARE},
+    {"tc_128x64x64_s8", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 64, 64, 8, 80, 197808, PYC_KERNEL_WORKLOAD_SMALL},
+    {"simt_128x128x16", GEMM_SIMT, (1 << PYC_DTYPE_F32) | (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 128, 16, 2, 30, 33792, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
+    {"simt_64x64x16", GEMM_SIMT, (1 << PYC_DTYPE_F32) | (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 64, 64, 16, 2, 20, 17408, PYC_KERNEL_WORKLOAD_SQUARE},
+    {"simt_32x64x16", GEMM_SIMT, (1 << PYC_DTYPE_F32) | (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 32, 64, 16, 2, 10, 13312, PYC_KERNEL_WORKLOAD_SMALL},
+};
+const GemmConfig* gemm_configs(int* count) {
+    *count = static_cast<int>(sizeof(kGemmConfigs) / sizeof(kGemmConfigs[0]));
+    return kGemmConfigs;
+}
+static const char* dtype_token(pyc_dtype d) { return d == PYC_DTYPE_F32 ? "f32" : d == PYC_DTYPE_BF16 ? "bf16" : d == PYC_DTYPE_F16 ? "f16" : "?"; }
+std::string gemm_symbol(pyc_dtype d, const GemmConfig& c) { return std::string("b200_gemm_") + dtype_token(d) + "_" + c.symbol; }
+
+// "b200_gemm_<dtype>_<suffix>" -> (dtype, config)
+static const GemmConfig* parse_gemm_symbol(const char* symbol, pyc_dtype* dt) {
+    static const char kPrefix[] = "b200_gemm_";
+    if (strncmp(symbol, kPrefix, sizeof(kPrefix) - 1) != 0) return nullptr;
+    const char* rest = symbol + sizeof(kPrefix) - 1;
+    const pyc_dtype cands[3] = {PYC_DTYPE_F32, PYC_DTYPE_BF16, PYC_DTYPE_F16};
+    for (pyc_dtype d : cands) {
+        const char* tok = dtype_token(d);
+        const size_t n = strlen(tok);
+        if (strncmp(rest, tok, n) == 0 && rest[n] == '_') {
+            for (const GemmConfig& c : kGemmConfigs)
+                if (strcmp(rest + n + 1, c.symbol) == 0 && (c.dtype_mask & (1 << d))) { *dt = d; return &c; }
+        }
+    }
+    return nullptr;
+}
+const GemmConfig* find_gemm_config(const char* symbol) {
+    pyc_dtype d;
+    return parse_gemm_symbol(symbol, &d);
+}
+
+static void reg_add(const char* op_key, const std::string& symbol, int priority, double occ, int tc, size_t smem, int regclass,
+                    pyc_kernel_workload_family wf) {
+    RegEntry e;
+    memset(&e, 0, sizeof(e));
+    strncpy(e.desc.op_key, op_key, PYC_KERNEL_OP_KEY_MAX - 1);
+    strncpy(e.desc.symbol, symbol.c_str(), PYC_KERNEL_SYMBOL_MAX - 1);
+    e.desc.backend = PYC_BACKEND_CUDA;
+    e.desc.priority = priority;
+    e.desc.estimated_occupancy = occ;
+    e.desc.tensor_core_eligible = tc;
+    e.desc.shared_mem_bytes = smem;
+    e.desc.reg_pressure_class = regclass;
+    e.desc.preferred_workload_family = wf;
+    // PyC's enum stops at HOPPER and maps compute capability >= 9 to it
+    // (cuda_backend.c:279-285), so that is the family a B200 reports.
+    e.desc.preferred_hardware_family = PYC_KERNEL_HARDWARE_HOPPER;
+    e.best_ms = 0.0;
+    g_reg.push_back(e);
+    if (pyc_kernel_register) pyc_kernel_register(&e.desc);
+}
+
+void registry_init_once() {
+    std::lock_guard<std::mutex> lk(g_reg_mu);
+    if (g_reg_done) return;
+    g_reg_done = true;
+    for (const GemmConfig& c : kGemmConfigs) {
+        const pyc_dtype cands[3] = {PYC_DTYPE_BF16, PYC_DTYPE_F16, PYC_DTYPE_F32};
+        for (pyc_dtype d : cands) {
+            if (!(c.dtype_mask & (1 << d))) continue;
+            // One CTA per SM (persistent) for the tensor-core kernels; SIMT tiles run 2-4 CTAs per SM.
+            int prio = c.priority;
+            if (c.kind == GEMM_SIMT && d != PYC_DTYPE_F32) prio -= 5;  // any-shape path for 16-bit types
+            reg_add("matmul", gemm_symbol(d, c), prio, c.kind == GEMM_TC ? 0.09 : 0.5, c.kind == GEMM_TC ? 1 : 0, c.smem_bytes,
+                    c.kind == GEMM_TC ? 2 : 1, c.workload);
+        }
+    }
+    reg_add("conv2d", "b200_conv2d_fprop_bf16", 100, 0.09, 1, 197744, 2, PYC_KERNEL_WORKLOAD_ANY);
+    reg_add("conv2d", "b200_conv2d_fprop_f16", 90, 0.09, 1, 197744, 2, PYC_KERNEL_WORKLOAD_ANY);
+    reg_add("attention", "b200_attention_bf16", 100, 0.09, 1, 200000, 3, PYC_KERNEL_WORKLOAD_ANY);
+    reg_add("attention", "b200_attention_bf16_causal", 95, 0.09, 1, 200000, 3, PYC_KERNEL_WORKLOAD_ANY);
+    reg_add("attention", "b200_attention_f16", 90, 0.09, 1, 200000, 3, PYC_KERNEL_WORKLOAD_ANY);
+    reg_add("attention", "b200_attention_f16_causal", 85, 0.09, 1, 200000, 3, PYC_KERNEL_WORKLOAD_ANY);
+
+    const char* promoted = getenv("PYC_PROMOTED_GEMM_SYMBOL");
+    if (promoted && promoted[0]) {
+        bool known = false;
+        for (const RegEntry& e : g_reg) known = known || (strcmp(e.desc.op_key, "matmul") == 0 && strcmp(e.desc.symbol, promoted) == 0);
+        if (known) {
+            g_promoted["matmul"] = promoted;
+            if (pyc_kernel_promote_symbol) pyc_kernel_promote_symbol("matmul", PYC_BACKEND_CUDA, promoted);
+        }
+    }
+}
+
+int registry_count(const char* op_key) {
+    registry_init_once();
+    if (!op_key) return 0;
+    if (pyc_kernel_collect) {
+        std::vector<pyc_kernel_desc> tmp(PYC_KERNEL_MAX);
+        return static_cast<int>(pyc_kernel_collect(op_key, PYC_BACKEND_CUDA, tmp.data(), tmp.size()));
+    }
+    std::lock_guard<std::mutex> lk(g_reg_mu);
+    int n = 0;
+    for (const RegEntry& e : g_reg) n += strcmp(e.desc.op_key, op_key) == 0;
+    return n;
+}
+
+bool registry_promoted_symbol(const char* op_key, std::string* out) {
+    registry_init_once();
+    if (pyc_kernel_promoted_symbol) {
+        char buf[PYC_KERNEL_SYMBOL_MAX] = "";
+        if (pyc_kernel_promoted_symbol(op_key, PYC_BACKEND_CUDA, buf, sizeof(buf)) == 0 && buf[0]) { *out = buf; return true; }
+    }
+    std::lock_guard<std::mutex> lk(g_reg_mu);
+    auto it = g_promoted.find(op_key);
+    if (it == g_promoted.end()) return false;
+    *out = it->second;
+    return true;
+}
+
+void registry_report_ms(const char* op_key, const char* symbol, double ms) {
+    registry_init_once();
+    {
+        std::lock_guard<std::mutex> lk(g_reg_mu);
+        for (RegEntry& e : g_reg)
+            if (strcmp(e.desc.op_key, op_key) == 0 && strcmp(e.desc.symbol, symbol) == 0 && (e.best_ms == 0.0 || ms < e.best_ms)) e.best_ms = ms;
+    }
+    if (pyc_kernel_benchmark_update_symbol) pyc_kernel_benchmark_update_symbol(op_key, PYC_BACKEND_CUDA, symbol, ms);
+}
+
+// ------------------------------------------------------- GEMM config choice --
+static std::mutex g_win_mu;
+static std::map<std::tuple<int, int, int, int>, const GemmConfig*> g_winners;
+
+void remember_gemm_winner(pyc_dtype dtype, int M, int N, int K, const GemmConfig* cfg) {
+    std::lock_guard<std::mutex> lk(g_win_mu);
+    g_winners[std::make_tuple(static_cast<int>(dtype), M, N, K)] = cfg;
+}
+
+bool gemm_config_supports(const GemmConfig& cfg, const GemmProblem& p) {
+    if (!(cfg.dtype_mask & (1 << p.dtype))) return false;
+    if (cfg.kind == GEMM_SIMT) return true;
+    // TMA: 16-byte aligned bases and row strides.
+    if (p.K % 8 != 0) return false;
+    if (!p.b_col_major && p.N % 8 != 0) return false;
+    if (reinterpret_cast<uintptr_t>(p.A) % 16 || reinterpret_cast<uintptr_t>(p.B) % 16) return false;
+    DeviceContext* c = current_context();
+    return c && c->cc_major == 10;
+}
+
+const GemmConfig* choose_gemm_config(const GemmProblem& p) {
+    {
+        std::lock_guard<std::mutex> lk(g_win_mu);
+        auto it = g_winners.find(std::make_tuple(static_cast<int>(p.dtype), p.M, p.N, p.K));
+        if (it != g_winners.end() && gemm_config_supports(*it->second, p)) return it->second;
+    }
+    std::string promoted;
+    if (registry_promoted_symbol("matmul", &promoted)) {
+        pyc_dtype d;
+        const GemmConfig* c = parse_gemm_symbol(promoted.c_str(), &d);
+        if (c && d == p.dtype && gemm_config_supports(*c, p)) return c;
+    }
+    // Shape heuristic: estimated time = waves * tile work / relative efficiency of the tile.
+    const int sms = sm_count();
+    const GemmConfig* best = nullptr;
+    double best_cost = 0.0;
+    for (const GemmConfig& c : kGemmConfigs) {
+        if (!gemm_config_supports(c, p)) continue;
+        const double tiles = static_cast<double>((p.M + c.bm - 1) / c.bm) * ((p.N + c.bn - 1) / c.bn);
+        double eff, slots;
+        if (c.kind == GEMM_TC) { eff = c.bn == 256 ? 1.0 : c.bn == 128 ? 0.85 : 0.6; slots = sms; }
+        else { eff = (c.bm == 128 ? 1.0 : c.bm == 64 ? 0.8 : 0.55) / 24.0; slots = sms * (c.bm == 128 ? 2.0 : 4.0); }
+        const double waves = static_cast<double>(static_cast<long long>((tiles + slots - 1) / slots));
+        const double cost = waves * c.bm * c.bn / eff;
+        if (!best || cost < best_cost) { best = &c; best_cost = cost; }
+    }
+    return best;
+}
+
+int launch_gemm(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream) {
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0 || !p.A || !p.B || !p.D) { set_error("gemm: bad shape or NULL pointer"); return -1; }
+    if (!gemm_config_supports(cfg, p)) { set_error("gemm: configuration %s does not support this dtype/shape/alignment", cfg.symbol); return -1; }
+    if (cfg.kind == GEMM_TC) {
+        int* st = device_status_word();
+        if (!st) return -1;
+        return launch_gemm_tc(cfg, p, stream, st);
+    }
+    return launch_gemm_simt(cfg, p, stream);
+}
+
+}  // namespace b200
+
+// ======================================================================== C API
+using namespace b200;
+
+extern "C" {
+
+void pyc_cutlass_registry_init(void) { registry_init_once(); }
+
+__attribute__((constructor)) static void b200_auto_register(void) { registry_init_once(); }
+
+int pyc_cutlass_kernel_count(const char* op_key) { return registry_count(op_key); }
+
+const char* pyc_b200_last_error(void) { return last_error(); }
+
+int pyc_cutlass_gemm_dispatch(const char* symbol, int M, int N, int K, const void* A, const void* B, void* C,
+                              float alpha, float beta, void* stream) {
+    if (!symbol) return -1;
+    GemmProblem p;
+    p.M = M; p.N = N; p.K = K; p.A = A; p.B = B; p.D = C; p.alpha = alpha;
+    if (beta != 0.0f) { p.add_mode = PYC_B200_ADD_MATRIX; p.add = C; p.add_scale = beta; }
+    const GemmConfig* cfg = nullptr;
+    pyc_dtype dt = PYC_DTYPE_UNKNOWN;
+    if ((cfg = parse_gemm_symbol(symbol, &dt)) != nullptr) {
+        p.dtype = dt;
+    } else if (strcmp(symbol, "cutlass_gemm_tensorcore_bf16") == 0) {
+        p.dtype = PYC_DTYPE_BF16;
+    } else if (strcmp(symbol, "cutlass_gemm_tensorcore_f16") == 0) {
+        p.dtype = PYC_DTYPE_F16; p.b_col_major = true;  // RowMajor x ColumnMajor, gemm/kernel.cu:48-65
+    } else if (strcmp(symbol, "cutlass_gemm_simt_f32") == 0 || strcmp(symbol, "ada_gemm_k64_warp32_async_f32") == 0) {
+        p.dtype = PYC_DTYPE_F32;
+    } else {
+        set_error("unknown GEMM symbol %s", symbol);
+        return -1;
+    }
+    if (!cfg) cfg = choose_gemm_config(p);
+    if (!cfg) { set_error("no GEMM configuration for this problem"); return -1; }
+    return launch_gemm(*cfg, p, static_cast<cudaStream_t>(stream));
+}
+
+int pyc_b200_gemm(const pyc_b200_gemm_args* a, void* stream) {
+    if (!a) return -1;
+    GemmProblem p;
+    p.dtype = a->dtype; p.M = a->M; p.N = a->N; p.K = a->K; p.A = a->A; p.B = a->B; p.D = a->D;
+    p.b_col_major = a->b_col_major != 0; p.alpha = a->alpha; p.add_mode = a->add_mode; p.add = a->add; p.act = a->act;
+    const GemmConfig* cfg = nullptr;
+    if (a->symbol && a->symbol[0]) {
+        pyc_dtype dt;
+        cfg = parse_gemm_symbol(a->symbol, &dt);
+        if (!cfg || dt != a->dtype) { set_error("GEMM symbol %s does not exist for this dtype", a->symbol); return -1; }
+    } else {
+        cfg = choose_gemm_config(p);
+    }
+    if (!cfg) { set_error("no GEMM configuration for this problem"); return -1; }
+    return launch_gemm(*cfg, p, static_cast<cudaStream_t>(stream));
+}
+
+int pyc_b200_add(pyc_dtype dtype, const void* a, const void* b, void* out, size_t elems, void* stream) {
+    return launch_add(dtype, a, b, out, elems, static_cast<cudaStream_t>(stream));
+}
+int pyc_b200_bias_act(pyc_dtype dtype, const void* x, const void* add, pyc_b200_add_mode add_mode, pyc_b200_activation act,
+                      void* out, size_t rows, size_t cols, void* stream) {
+    return launch_bias_act(dtype, x, add, add_mode, act, out, rows, cols, static_cast<cudaStream_t>(stream));
+}
+int pyc_b200_layernorm(pyc_dtype dtype, const void* x, const void* gamma, const void* beta, void* out, size_t rows, size_t cols,
+                       float eps, void* stream) {
+    return launch_layernorm(dtype, x, gamma, beta, out, rows, cols, eps, static_cast<cudaStream_t>(stream));
+}
+int pyc_b200_softmax(pyc_dtype dtype, const void* x, void* out, size_t rows, size_t cols, void* stream) {
+    return launch_softmax(dtype, x, out, rows, cols, static_cast<cudaStream_t>(stream));
+}
+int pyc_b200_reduce_sum(pyc_dtype dtype, const void* x, void* out, size_t rows, size_t cols, void* stream) {
+    return launch_reduce_sum(dtype, x, out, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+int pyc_b200_autotune_gemm(pyc_dtype dtype, int M, int N, int K, int iters, char* best_symbol, size_t best_symbol_size, double* best_ms) {
+    DeviceContext* ctx = current_context();
+    if (!ctx || M <= 0 || N <= 0 || K <= 0) return -1;
+    if (iters < 1) iters = 3;
+    const size_t es = dtype_size(dtype);
+    if (!es) { set_error("autotune: unsupported dtype"); return -1; }
+    void *A = nullptr, *B = nullptr, *D = nullptr;
+    if (cudaMalloc(&A, es * M * K) != cudaSuccess || cudaMalloc(&B, es * K * N) != cudaSuccess || cudaMalloc(&D, es * M * N) != cudaSuccess) {
+        cudaGetLastError(); cudaFree(A); cudaFree(B); cudaFree(D); set_error("autotune: out of device memory"); return -1;
+    }
+    cudaMemset(A, 0, es * M * K); cudaMemset(B, 0, es * K * N);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    GemmProblem p;
+    p.dtype = dtype; p.M = M; p.N = N; p.K = K; p.A = A; p.B = B; p.D = D;
+    int timed = 0;
+    const GemmConfig* best = nullptr;
+    double best_t = 0.0;
+    int n = 0;
+    const GemmConfig* cfgs = gemm_configs(&n);
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    for (int i = 0; i < n; ++i) {
+        if (!gemm_config_supports(cfgs[i], p)) continue;
+        // The SIMT tiles are only worth timing for fp32 or when no tensor-core tile fits.
+        if (cfgs[i].kind == GEMM_SIMT && dtype != PYC_DTYPE_F32 && best) continue;
+        if (launch_gemm(cfgs[i], p, ctx->stream) != 0) continue;  // warm-up
+        double t = 1e30;
+        for (int it = 0; it < iters; ++it) {
+            cudaEventRecord(e0, ctx->stream);
+            launch_gemm(cfgs[i], p, ctx->stream);
+            cudaEventRecord(e1, ctx->stream);
+            if (cudaEventSynchronize(e1) != cudaSuccess) { t = 1e30; break; }
+            float ms = 0.0f;
+            cudaEventElapsedTime(&ms, e0, e1);
+            if (ms < t) t = ms;
+        }
+        if (t >= 1e30) continue;
+        registry_report_ms("matmul", gemm_symbol(dtype, cfgs[i]).c_str(), t);
+        ++timed;
+        if (!best || t < best_t) { best = &cfgs[i]; best_t = t; }
+    }
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaFree(A); cudaFree(B); cudaFree(D);
+    if (!best) { set_error("autotune: no configuration ran"); return -1; }
+    remember_gemm_winner(dtype, M, N, K, best);
+    if (best_symbol && best_symbol_size) { strncpy(best_symbol, gemm_symbol(dtype, *best).c_str(), best_symbol_size - 1); best_symbol[best_symbol_size - 1] = 0; }
+    if (best_ms) *best_ms = best_t;
+    return timed;
+}
+
+int pyc_b200_get_runtime_info(pyc_b200_runtime_info* out) {
+    if (!out) return -1;
+    memset(out, 0, sizeof(*out));
+    out->kernel_launches_total = launches_total();
+    DeviceContext* c = current_context();
+    if (!c) return -1;
+    std::lock_guard<std::mutex> lk(c->mu);
+    out->arena_bytes = c->arena_bytes;
+    out->plan_peak_bytes = c->last_plan_peak;
+    out->plan_total_bytes = c->last_plan_total;
+    out->graphs_cached = c->graphs.size();
+    out->graph_replays = c->graph_replays;
+    out->kernels_per_graph = c->last_graph_kernels;
+    return 0;
+}
+
+int pyc_b200_set_stream(void* stream, int async) {
+    DeviceContext* c = current_context();
+    if (!c) return -1;
+    std::lock_guard<std::mutex> lk(c->mu);
+    c->user_stream = static_cast<cudaStream_t>(stream);
+    c->use_user_stream = stream != nullptr || async != 0;
+    c->async = async != 0;
+    return 0;
+}
+
+int pyc_b200_device_status(void) {
+    DeviceContext* c = current_context();
+    if (!c) return -1;
+    std::lock_guard<std::mutex> lk(c->mu);
+    return read_device_status(c->stream);
+}
+
+void pyc_b200_shutdown(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return; }
+    DeviceContext* c = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_ctx_mu);
+        c = g_ctx[dev];
+        g_ctx[dev] = nullptr;
+    }
+    if (!c) return;
+    cudaDeviceSynchronize();
+    c->drop_graphs();
+    if (c->arena) cudaFree(c->arena);
+    if (c->pinned) cudaFreeHost(c->pinned);
+    if (c->status_dev) cudaFree(c->status_dev);
+    if (c->status_host) cudaFreeHost(c->status_host);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+}  // extern "C"

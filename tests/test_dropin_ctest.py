@@ -1,0 +1,23 @@
+"""CPU: PyC's own C tests for the seam, compiled from PyC's sources by
+oracle/Makefile and linked against PyC's front half + THIS backend instead of
+PyC's cuda_backend.c.  They pass unchanged, which is the drop-in claim.  The
+binaries only exist where a PyC checkout was available at build time."""
+import glob
+import os
+import subprocess
+
+import pytest
+
+REF = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref")
+BINARIES = sorted(glob.glob(os.path.join(REF, "ctest_*")))
+
+
+@pytest.mark.skipif(not BINARIES, reason="PyC's tests were not built (no PyC checkout at build time)")
+@pytest.mark.parametrize("path", BINARIES, ids=[os.path.basename(p) for p in BINARIES])
+def test_pyc_ctest_passes_against_this_backend(path, tmp_path):
+    env = dict(os.environ)
+    for k in ["PYC_CUDA_DISABLE", "PYC_CUDA_FORCE_ERROR", "PYC_CUDA_FORCE_FALLBACK", "PYC_CUDA_SIMULATE_AVAILABLE"]:
+        env.pop(k, None)
+    env["PYC_AUTOTUNE_DB_PATH"] = str(tmp_path / "autotune.db")
+    r = subprocess.run([path], cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, f"{os.path.basename(path)} exited {r.returncode}\n{r.stdout[-2000:]}\n{r.stderr[-2000:]}"
