@@ -556,7 +556,13 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
         const cudaError_t se = cudaStreamSynchronize(launch_stream);
         if (trace) trace->sync_ms = now_ms() - t0;
         if (se != cudaSuccess) { snprintf(reason, reason_size, "b200_sync_failed:%s", cudaGetErrorString(se)); cudaGetLastError(); return -1; }
-        if (*ctx->status_host != 0) { snprintf(reason, reason_size, "b200_kernel_wait_timeout:0x%x", *ctx->status_host); return -1; }
+        if (*ctx->status_host != 0) {
+            snprintf(reason, reason_size, "b200_kernel_wait_timeout:0x%x", *ctx->status_host);
+            cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), launch_stream);
+            cudaStreamSynchronize(launch_stream);
+            *ctx->status_host = 0;
+            return -1;
+        }
         t0 = now_ms();
         for (const Step& s : plan.steps)
             if (s.kind == S_D2H && s.via_stage) memcpy(outputs[s.ext].data, static_cast<char*>(ctx->pinned) + s.stage_off, s.bytes);

@@ -95,7 +95,13 @@ int read_device_status(cudaStream_t stream) {
     if (!c) return -1;
     if (cudaMemcpyAsync(c->status_host, c->status_dev, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return -1;
     if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;
-    return *c->status_host;
+    const int st = *c->status_host;
+    if (st != 0) {  // read-and-clear, so one timed-out wait is reported once
+        cudaMemsetAsync(c->status_dev, 0, sizeof(int), stream);
+        cudaStreamSynchronize(stream);
+        *c->status_host = 0;
+    }
+    return st;
 }
 
 int DeviceContext::ensure_arena(size_t bytes) {
