@@ -12,7 +12,6 @@ collective on the data path).  One JSON line is printed by rank 0.
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -37,37 +36,82 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and throttle reasons (read-only NVML queries, ~every 2 ms) in a thread; only
+    samples taken inside a window opened with begin()/end() -- the timed regions -- are reported."""
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.samples, self.windows, self._stop, self.thread, self.err = index, [], [], False, None, None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = None
+            try:
+                import torch
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            except Exception:
+                pass
+            h = None
+            if uuid:
+                for i in range(pynvml.nvmlDeviceGetCount()):
+                    hi = pynvml.nvmlDeviceGetHandleByIndex(i)
+                    u = pynvml.nvmlDeviceGetUUID(hi)
+                    u = u.decode() if isinstance(u, bytes) else u
+                    if uuid in u:
+                        h = hi
+            self.h = h or pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.nv = pynvml
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # no NVML: report that, never guess
+            self.err = f"nvml unavailable: {e}"
+            return
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _run(self):
+        nv = self.nv
+        while not self._stop:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                try:
+                    watts = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                except Exception:
+                    watts = None
+                self.samples.append((time.perf_counter(), mhz, reasons, watts))
+            except Exception as e:
+                self.err = str(e)
+                return
+            time.sleep(0.002)
+
+    def begin(self):
+        self._t0 = time.perf_counter()
+
+    def end(self):
+        self.windows.append((self._t0, time.perf_counter()))
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        self.thread.join(timeout=2)
-        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
-        mx = next((int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()), None)
-        # the sampler only runs while the GPU is busy (warm-up + timed regions), so the plain median is "under load"
-        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": reasons, "samples": len(mhz)}
+        self._stop = True
+        if self.thread:
+            self.thread.join(timeout=2)
+        if self.err and not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.err]}
+        inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in self.windows)]
+        mhz = sorted(s[1] for s in inside)
+        bits = 0
+        for s in inside:
+            bits |= int(s[2])
+        nv = self.nv
+        names = [("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4),
+                 ("hw_power_brake", 0x80), ("sync_boost", 0x10), ("applications_clocks_setting", 0x2)]
+        reasons = [n for n, m in names if bits & m]
+        watts = [s[3] for s in inside if s[3] is not None]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_min_mhz": mhz[0] if mhz else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(mhz), "power_w_max": max(watts) if watts else None}
 
 
 def build_problem(torch, rank):
@@ -198,11 +242,13 @@ def main():
     barrier()
     launches0 = backend.runtime_info().kernel_launches_total
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.begin()
     e0.record(stream)
     for _ in range(args.steps):
         st, trace = backend.dispatch(module, ins, outs)
     e1.record(stream)
     barrier()
+    sampler.end()
     ms_total = e0.elapsed_time(e1)
     launches = backend.runtime_info().kernel_launches_total - launches0
     assert backend.device_status() == 0, "a kernel wait timed out"
@@ -215,11 +261,13 @@ def main():
     for _ in range(2):
         backend.dispatch(module, h_ins, h_outs)
     barrier()
+    sampler.begin()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         backend.dispatch(module, h_ins, h_outs)
     barrier()
     e2e_s = time.perf_counter() - t0
+    sampler.end()
     clocks = sampler.stop()
     same = bool((out_host[:64].to(torch.int32) == out_dev[:64].cpu().to(torch.int32)).all())
 
