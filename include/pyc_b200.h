@@ -134,6 +134,22 @@ typedef struct {
 } pyc_b200_gemm_args;
 int pyc_b200_gemm(const pyc_b200_gemm_args* args, void* stream);
 
+/* No counterpart in PyC.  The same tensor-core GEMM (bf16 / f16 only) for callers
+ * that cannot allocate device memory when they need it: hosts that have given
+ * all of HBM to their own pool, threads that must not trigger the device-wide
+ * synchronisation of an allocation, code that runs while a capture is open.
+ * It creates no context, stream or buffer and calls no allocator; the kernel's
+ * only scratch (its status block) is a 256-byte array compiled into the library
+ * and resident on every GPU that loads it.  Limits: M, N, K <= 1048576 each,
+ * K % 8 == 0, N % 8 == 0 for row-major B, A and B 16-byte aligned; anything
+ * else returns -1 with a message in pyc_b200_last_error().  The first call on a
+ * device does one-time set-up (address of the array, kernel attributes): make it
+ * before any stream capture.  All calls share the array and clear it on
+ * `stream` before launching, so calls whose kernels overlap on the GPU race on
+ * it: issue them on one stream or order them with events.  args->symbol is
+ * ignored (the tile width is chosen from the shape). */
+int pyc_b200_gemm_static(const pyc_b200_gemm_args* args, void* stream);
+
 /* Elementwise / reduction ops on device pointers (HBM-bound kernels). */
 int pyc_b200_add(pyc_dtype dtype, const void* a, const void* b, void* out, size_t elems, void* stream);
 int pyc_b200_bias_act(pyc_dtype dtype, const void* x, const void* add, pyc_b200_add_mode add_mode,

@@ -19,7 +19,7 @@ EXPORTS = [
     "pyc_cutlass_gemm_dispatch", "pyc_cutlass_conv2d_dispatch", "pyc_cutlass_attention_dispatch",
     "pyc_cutlass_kernel_count", "pyc_cutlass_registry_init",
     # additive
-    "pyc_b200_gemm", "pyc_b200_add", "pyc_b200_bias_act", "pyc_b200_layernorm", "pyc_b200_softmax",
+    "pyc_b200_gemm", "pyc_b200_gemm_static", "pyc_b200_add", "pyc_b200_bias_act", "pyc_b200_layernorm", "pyc_b200_softmax",
     "pyc_b200_reduce_sum", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm",
     "pyc_b200_get_runtime_info", "pyc_b200_set_stream", "pyc_b200_device_status", "pyc_b200_last_error",
     "pyc_b200_shutdown",
@@ -53,6 +53,7 @@ def load():
     L.pyc_cutlass_kernel_count.argtypes = [C.c_char_p]
     L.pyc_cutlass_registry_init.restype = None
     L.pyc_b200_gemm.argtypes = [C.POINTER(abi.GemmArgs), vp]
+    L.pyc_b200_gemm_static.argtypes = [C.POINTER(abi.GemmArgs), vp]
     L.pyc_b200_add.argtypes = [i, vp, vp, vp, sz, vp]
     L.pyc_b200_bias_act.argtypes = [i, vp, vp, i, i, vp, sz, sz, vp]
     L.pyc_b200_layernorm.argtypes = [i, vp, vp, vp, vp, sz, sz, f, vp]
@@ -124,6 +125,20 @@ def gemm(dtype, M, N, K, A, B, D, add=None, add_mode=abi.ADD_NONE, act=abi.ACT_N
     a.add = add
     a.act = act
     _check(load().pyc_b200_gemm(C.byref(a), stream), "pyc_b200_gemm")
+
+
+def gemm_static(dtype, M, N, K, A, B, D, add=None, add_mode=abi.ADD_NONE, act=abi.ACT_NONE, alpha=1.0, b_col_major=False, stream=0):
+    """pyc_b200_gemm_static: the tensor-core GEMM without any allocation (see include/pyc_b200.h)."""
+    a = abi.GemmArgs()
+    a.symbol = None
+    a.dtype, a.M, a.N, a.K = dtype, M, N, K
+    a.A, a.B, a.D = A, B, D
+    a.b_col_major = int(b_col_major)
+    a.alpha = alpha
+    a.add_mode = add_mode if add else abi.ADD_NONE
+    a.add = add
+    a.act = act
+    _check(load().pyc_b200_gemm_static(C.byref(a), stream), "pyc_b200_gemm_static")
 
 
 def add(dtype, a, b, out, elems, stream=0):

@@ -23,6 +23,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "internal.h"
 #include "ptx_sm100.cuh"
 
@@ -322,4 +324,131 @@ int launch_gemm_tc(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t str
     return -1;
 }
 
+// ---------------------------------------------------------------------------
+// pyc_b200_gemm_static: the same tensor-core GEMM for callers that must not
+// allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they
+// need a GEMM: a serving loop that has already handed all device memory to its
+// own pool (PyC's Rust runtime keeps such a pool), code running while a stream
+// capture is open elsewhere in the process, or a latency-critical thread that
+// cannot afford the device-wide synchronisation an allocation implies.  The
+// ordinary entry points create a per-device context on first use (stream,
+// status word, pinned mirror).  This one touches none of that: the only scratch
+// the kernel needs -- the status block its bounded waits report into -- lives
+// in the file-scope device array below, which every GPU that loads the library
+// holds (256 bytes) until the process exits.
+//
+// The first call on each device resolves the array's device address with
+// cudaGetSymbolAddress (the name below is only a host-side handle, not a device
+// pointer), raises the kernel's dynamic shared-memory limit and reads the SM
+// count.  Make that first call before any stream capture begins.  Every call
+// shares the one block and clears it on `stream` before launching, so two calls
+// whose kernels overlap on the GPU (different streams) race on it: keep calls
+// on one stream, or order them with events.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int kStaticScratchBytes = 256;
+constexpr int kStaticMaxDim = 1 << 20;  // largest M, N or K accepted; the kernel's 32-bit tile arithmetic is checked up to here
+static __device__ __align__(256) int g_static_scratch[kStaticScratchBytes / sizeof(int)];
+
+struct StaticDeviceSetup {
+    bool ready = false;
+    int* scratch = nullptr;  // device address of g_static_scratch on this device
+    int sms = 0;
+    bool attr[3][2][2] = {};
+};
+StaticDeviceSetup g_static_setup[16];
+
+template <int BN, int STAGES, bool B_KMAJOR, int FMT>
+int launch_static_instance(const GemmProblem& p, cudaStream_t stream, StaticDeviceSetup& sd, int bn_index) {
+    auto kernel = gemm_tc_kernel<BN, STAGES, B_KMAJOR, FMT>;
+    constexpr size_t smem = tc_smem_bytes<BN, STAGES>();
+    if (!sd.attr[bn_index][B_KMAJOR ? 1 : 0][FMT]) {
+        B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        sd.attr[bn_index][B_KMAJOR ? 1 : 0][FMT] = true;
+    }
+    CUtensorMap tmA, tmB;
+    if (encode_tmap_2d(&tmA, p.A, 2, p.M, p.K, static_cast<uint64_t>(p.K) * 2, BM, BK) != 0) return -1;
+    if (B_KMAJOR) {
+        if (encode_tmap_2d(&tmB, p.B, 2, p.N, p.K, static_cast<uint64_t>(p.K) * 2, BN, BK) != 0) return -1;
+    } else {
+        if (encode_tmap_2d(&tmB, p.B, 2, p.K, p.N, static_cast<uint64_t>(p.N) * 2, BK, 64) != 0) return -1;
+    }
+    Epilogue ep;
+    ep.D = p.D; ep.add = p.add; ep.alpha = p.alpha; ep.add_scale = p.add_scale;
+    ep.add_mode = p.add ? p.add_mode : PYC_B200_ADD_NONE; ep.act = p.act;
+    ep.vec_ok = ((reinterpret_cast<uintptr_t>(p.D) % 16 == 0) && (p.N % 8 == 0) &&
+                 (ep.add_mode == PYC_B200_ADD_NONE || ep.add_mode == PYC_B200_ADD_SCALAR || reinterpret_cast<uintptr_t>(p.add) % 16 == 0)) ? 1 : 0;
+    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    // The block keeps whatever the previous call left: the status word must start at zero.
+    B200_CUDA_OK(cudaMemsetAsync(sd.scratch, 0, kStaticScratchBytes, stream));
+    kernel<<<tiles < sd.sms ? tiles : sd.sms, 192, smem, stream>>>(tmA, tmB, ep, p.M, p.N, p.K, sd.scratch);
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+template <int BN, int STAGES>
+int launch_static_layout(const GemmProblem& p, cudaStream_t stream, StaticDeviceSetup& sd, int bn_index) {
+    const bool bf16 = p.dtype == PYC_DTYPE_BF16;
+    if (p.b_col_major) return bf16 ? launch_static_instance<BN, STAGES, true, 1>(p, stream, sd, bn_index) : launch_static_instance<BN, STAGES, true, 0>(p, stream, sd, bn_index);
+    return bf16 ? launch_static_instance<BN, STAGES, false, 1>(p, stream, sd, bn_index) : launch_static_instance<BN, STAGES, false, 0>(p, stream, sd, bn_index);
+}
+
+}  // namespace
 }  // namespace b200
+
+extern "C" int pyc_b200_gemm_static(const pyc_b200_gemm_args* a, void* stream) {
+    using namespace b200;
+    if (!a || !a->A || !a->B || !a->D) { set_error("pyc_b200_gemm_static: NULL argument"); return -1; }
+    if (a->dtype != PYC_DTYPE_BF16 && a->dtype != PYC_DTYPE_F16) { set_error("pyc_b200_gemm_static: only bf16 and f16 (the tensor-core kernel)"); return -1; }
+    if (a->M <= 0 || a->N <= 0 || a->K <= 0) { set_error("pyc_b200_gemm_static: M, N, K must be positive"); return -1; }
+    if (a->M > kStaticMaxDim || a->N > kStaticMaxDim || a->K > kStaticMaxDim) {
+        set_error("pyc_b200_gemm_static: %dx%dx%d exceeds the supported maximum of %d per dimension", a->M, a->N, a->K, kStaticMaxDim);
+        return -1;
+    }
+    if (a->K % 8 != 0 || (!a->b_col_major && a->N % 8 != 0) || reinterpret_cast<uintptr_t>(a->A) % 16 || reinterpret_cast<uintptr_t>(a->B) % 16) {
+        set_error("pyc_b200_gemm_static: needs K %% 8 == 0, N %% 8 == 0 for row-major B, and 16-byte aligned A and B (TMA)");
+        return -1;
+    }
+    int dev = 0;
+    B200_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16) { set_error("pyc_b200_gemm_static: device index %d out of range", dev); return -1; }
+    StaticDeviceSetup& sd = g_static_setup[dev];
+    static std::mutex* setup_mu = new std::mutex();
+    std::lock_guard<std::mutex> setup_lock(*setup_mu);  // set-up and the shared block's clear+launch pair stay ordered per process
+    if (!sd.ready) {
+        // Once per device, with that device current.  The symbol name is a host-side stand-in; the kernel
+        // needs the address the driver reports for this device.
+        int major = 0, sms = 0;
+        B200_CUDA_OK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        B200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (major != 10) { set_error("pyc_b200_gemm_static: needs an sm_100 device, found compute capability major %d", major); return -1; }
+        void* ptr = nullptr;
+        B200_CUDA_OK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        if (!ptr) { set_error("pyc_b200_gemm_static: cudaGetSymbolAddress returned NULL"); return -1; }
+        sd.scratch = static_cast<int*>(ptr);
+        sd.sms = sms;
+        sd.ready = true;
+    }
+    GemmProblem p;
+    p.dtype = a->dtype; p.M = a->M; p.N = a->N; p.K = a->K; p.A = a->A; p.B = a->B; p.D = a->D;
+    p.b_col_major = a->b_col_major != 0; p.alpha = a->alpha; p.add_mode = a->add_mode; p.add = a->add; p.act = a->act;
+    // Tile width by the same wave-count estimate the allocating path uses.
+    int best_bn = 256;
+    double best_cost = 0.0;
+    const int bns[3] = {256, 128, 64};
+    const double eff[3] = {1.0, 0.85, 0.6};
+    for (int i = 0; i < 3; ++i) {
+        const double tiles = static_cast<double>((p.M + 127) / 128) * ((p.N + bns[i] - 1) / bns[i]);
+        const double waves = static_cast<double>(static_cast<long long>((tiles + sd.sms - 1) / sd.sms));
+        const double cost = waves * 128 * bns[i] / eff[i];
+        if (i == 0 || cost < best_cost) { best_cost = cost; best_bn = bns[i]; }
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (best_bn == 256) return launch_static_layout<256, 4>(p, s, sd, 0);
+    if (best_bn == 128) return launch_static_layout<128, 6>(p, s, sd, 1);
+    return launch_static_layout<64, 8>(p, s, sd, 2);
+}
