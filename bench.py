@@ -24,6 +24,9 @@ sys.path.insert(0, ROOT)
 M = N = K = 8192
 FLOP_PER_STEP = 2.0 * M * N * K
 ALGO_BYTES = 3 * M * N * 2 + N * 2          # A, B, D bf16 + bias
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of this exact shape, from the ncu capture summarised in
+# profiles/gemm_tc_bf16_8192x8192x8192_traffic.md (update both together when the kernel changes).
+NCU_TRAFFIC_BYTES = 1005495296 + 123691008
 METRIC = "fused bf16 GEMM+bias+GELU TFLOP/s via pyc_cuda_dispatch"
 
 
@@ -296,9 +299,7 @@ def main():
                     "ms_per_step": e2e_ms / e2e_steps, "h2d_bytes_per_step": (M * K + K * N + N) * 2, "d2h_bytes_per_step": M * N * 2},
             "gpu_launches": int(launches), "clocks": clocks,
         }
-        traffic_file = os.path.join(ROOT, "profiles", "gemm_tc_traffic.json")
-        if os.path.exists(traffic_file):
-            line["roofline"]["traffic"] = json.load(open(traffic_file)).get("dram_bytes_per_launch_8192")
+        line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES
         if not args.no_cpu_baseline:
             line["cpu_baseline"], _, _ = cpu_baseline()
         print(json.dumps(line), flush=True)
