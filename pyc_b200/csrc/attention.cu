@@ -1,0 +1,411 @@
+// Fused attention forward: Out = softmax(scale * Q K^T [+ causal mask]) V, online
+// softmax with fp32 statistics, both contractions on the tcgen05 tensor cores.
+//
+// Replaces PyC's attention "kernel", whose body copies Q to the output
+// (src/compiler/cutlass_kernels/attention/kernel.cu:30-59); the definition
+// implemented here is the one in that file's header comment (:6-8), with an
+// optional causal mask (key index <= query index).
+//
+// One CTA per (batch*head, block of 128 queries), 192 threads:
+//   warp 0     TMA producer: Q once, then K and V blocks of 128 keys (2-deep rings)
+//   warp 1     TMEM owner + single-thread MMA issuer:
+//                S[j&1] = Q K_j^T        (128x128xD,  S in TMEM, double buffered)
+//                O     += P_j V_j        (128xDx128,  O in TMEM, V as MN-major operand)
+//   warps 2-5  softmax, one query row per thread: S row from TMEM (two passes of
+//              32-column chunks: max, then exp2/sum), P_j -> bf16 -> shared memory
+//              in the 128-byte-swizzled K-major operand layout, O rescaled in TMEM
+//              only when some row's running max moved.
+// QK^T of block j+1 is issued before the issuer waits for P_j, so the tensor pipe
+// works under the softmax of block j.  Causal blocks above the diagonal are never
+// loaded or multiplied.  Every wait is bounded (status word, see ptx_sm100.cuh).
+//
+// Layout: Q, K, V, Out are [batch_heads, seq, d] contiguous; tensor maps are 3-D
+// (d, seq, batch_heads) so rows past `seq` read as zeros instead of the next head.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <string.h>
+
+#include "internal.h"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int BQ = 128;   // queries per CTA
+constexpr int BKV = 128;  // keys per block
+
+template <int FMT> struct AElem;
+template <> struct AElem<1> {
+    using T = __nv_bfloat16;
+    static __device__ __forceinline__ uint32_t pack(float a, float b) { __nv_bfloat162 p = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&p); }
+};
+template <> struct AElem<0> {
+    using T = __half;
+    static __device__ __forceinline__ uint32_t pack(float a, float b) { __half2 p = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&p); }
+};
+
+struct AttnParams {
+    int seq, batch_heads, causal;
+    float scale_log2;  // scale * log2(e)
+    void* out;
+};
+
+// Shared-memory map (HD = 128): Q 32 KB | K 2 x 32 KB | V 2 x 32 KB | P 32 KB | barriers
+template <int HD>
+struct AttnSmem {
+    static constexpr int TILE = BQ * HD * 2;       // one [128 x HD] 16-bit tile
+    static constexpr int P_BYTES = BQ * BKV * 2;
+    static constexpr int Q_OFF = 0, K_OFF = TILE, V_OFF = 3 * TILE, P_OFF = 5 * TILE, BAR_OFF = 5 * TILE + P_BYTES;
+    static constexpr int NUM_BARS = 16;
+    static constexpr size_t BYTES = 1024 + BAR_OFF + NUM_BARS * 8 + 16;
+};
+
+template <int HD, int FMT>
+__global__ void __launch_bounds__(192, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, AttnParams ap, int* status) {
+    using SM = AttnSmem<HD>;
+    using E = AElem<FMT>;
+    using T = typename E::T;
+    constexpr int HALVES = HD / 64;                 // 64-column (128-byte) operand slabs per tile
+    constexpr int HALF_BYTES = BQ * 128;            // [128 rows x 128 B]
+    constexpr uint32_t IDESC_QK = make_idesc(FMT, FMT, 0, 0, BQ, BKV);
+    constexpr uint32_t IDESC_PV = make_idesc(FMT, FMT, 0, 1, BQ, HD);
+    constexpr uint32_t TMEM_COLS = 512;             // S0 @0, S1 @128, O @256
+    constexpr uint32_t O_COL = 256;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + SM::NUM_BARS);
+    const uint32_t bar0 = smem_u32(bars);
+    // barrier indices
+    const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 24, v_full = bar0 + 40, v_empty = bar0 + 56,
+                   s_full = bar0 + 72, s_empty = bar0 + 88, p_full = bar0 + 104, pv_done = bar0 + 112;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_qb = (ap.seq + BQ - 1) / BQ;
+    const int qb = num_qb - 1 - static_cast<int>(blockIdx.x);  // longest (causal) blocks first
+    const int bh = blockIdx.y;
+    const int q0 = qb * BQ;
+    const int kv_blocks_all = (ap.seq + BKV - 1) / BKV;
+    const int nblk = ap.causal ? min(kv_blocks_all, qb + 1) : kv_blocks_all;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full + 8 * i, 1); mbar_init(k_empty + 8 * i, 1);
+            mbar_init(v_full + 8 * i, 1); mbar_init(v_empty + 8 * i, 1);
+            mbar_init(s_full + 8 * i, 1); mbar_init(s_empty + 8 * i, 4);
+        }
+        mbar_init(p_full, 4);
+        mbar_init(pv_done, 1);
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    const uint32_t sQ = smem_u32(smem + SM::Q_OFF), sK = smem_u32(smem + SM::K_OFF), sV = smem_u32(smem + SM::V_OFF), sP = smem_u32(smem + SM::P_OFF);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, SM::TILE);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) tma_load_3d(sQ + h * HALF_BYTES, &tmQ, q_full, h * 64, q0, bh);
+            for (int j = 0; j < nblk; ++j) {
+                const int st = j & 1;
+                const uint32_t par = ((j >> 1) & 1) ^ 1;
+                if (!mbar_wait(k_empty + 8 * st, par, status, 0x21)) break;
+                mbar_arrive_expect_tx(k_full + 8 * st, SM::TILE);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) tma_load_3d(sK + st * SM::TILE + h * HALF_BYTES, &tmK, k_full + 8 * st, h * 64, j * BKV, bh);
+                if (!mbar_wait(v_empty + 8 * st, par, status, 0x22)) break;
+                mbar_arrive_expect_tx(v_full + 8 * st, SM::TILE);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) tma_load_3d(sV + st * SM::TILE + h * HALF_BYTES, &tmV, v_full + 8 * st, h * 64, j * BKV, bh);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            auto issue_qk = [&](int j) {  // S[j&1] = Q K_j^T
+                const int st = j & 1;
+                const uint32_t d = tmem_base + (j & 1) * BKV;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t off = (ks / 4) * HALF_BYTES + (ks % 4) * 32;
+                    umma_f16(d, make_smem_desc_sw128(sQ + off, 16, 1024), make_smem_desc_sw128(sK + st * SM::TILE + off, 16, 1024), IDESC_QK, ks != 0);
+                }
+                umma_commit(s_full + 8 * (j & 1));
+                umma_commit(k_empty + 8 * st);
+            };
+            bool ok = mbar_wait(q_full, 0, status, 0x23) && mbar_wait(k_full, 0, status, 0x24);
+            if (ok) { tc_fence_after(); issue_qk(0); }
+            for (int j = 0; j < nblk && ok; ++j) {
+                if (j + 1 < nblk) {
+                    const int jn = j + 1;
+                    if (!mbar_wait(k_full + 8 * (jn & 1), (jn >> 1) & 1, status, 0x25)) { ok = false; break; }
+                    if (!mbar_wait(s_empty + 8 * (jn & 1), ((jn >> 1) & 1) ^ 1, status, 0x26)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_qk(jn);
+                }
+                const int st = j & 1;
+                if (!mbar_wait(v_full + 8 * st, (j >> 1) & 1, status, 0x27)) { ok = false; break; }
+                if (!mbar_wait(p_full, j & 1, status, 0x28)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < BKV / 16; ++ks) {  // O += P_j V_j
+                    const uint64_t adesc = make_smem_desc_sw128(sP + (ks / 4) * HALF_BYTES + (ks % 4) * 32, 16, 1024);
+                    const uint64_t bdesc = make_smem_desc_sw128(sV + st * SM::TILE + ks * 2048, HALF_BYTES, 1024);
+                    umma_f16(tmem_base + O_COL, adesc, bdesc, IDESC_PV, (j | ks) != 0 ? 1u : 0u);
+                }
+                umma_commit(v_empty + 8 * st);
+                umma_commit(pv_done);
+            }
+        }
+    } else {
+        const int wq = warp & 3;
+        const int row = wq * 32 + lane;            // query row inside the block == TMEM lane
+        const int qi = q0 + row;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(wq * 32) << 16);
+        float m_run = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < nblk && ok; ++j) {
+            const uint32_t s_addr = lane_addr + (j & 1) * BKV;
+            if (!mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1, status, 0x29)) { ok = false; break; }
+            tc_fence_after();
+            const int k0 = j * BKV;
+            // keys this row may see in this block: [k0, k_lim)
+            int k_lim = ap.seq;
+            if (ap.causal) k_lim = min(k_lim, qi + 1);
+            // pass 1: row max
+            float m_blk = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(s_addr + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int t = 0; t < 32; ++t) if (k0 + c * 32 + t < k_lim) m_blk = fmaxf(m_blk, __uint_as_float(r[t]));
+            }
+            m_blk *= ap.scale_log2;  // scale > 0: max commutes with the scaling
+            const float m_new = fmaxf(m_run, m_blk);
+            const float m_use = m_new == -INFINITY ? 0.0f : m_new;  // fully masked so far: keep exp2 arguments finite
+            const float alpha = exp2f(m_run - m_use);                // m_run = -inf -> 0
+            // P and O are shared with the previous block's P*V: wait until it has finished.
+            if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, status, 0x2a)) { ok = false; break; }
+            tc_fence_after();
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {  // rescale this warp's 32 rows of O in TMEM
+#pragma unroll 1
+                for (int c = 0; c < HD / 16; ++c) {
+                    uint32_t o[16];
+                    tmem_ld_32x16(lane_addr + O_COL + c * 16, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * alpha);
+                    tmem_st_32x16(lane_addr + O_COL + c * 16, o);
+                }
+                tmem_st_wait();
+            }
+            // pass 2: exponentiate, sum, write P (16-bit) into the swizzled K-major operand tile
+            float l_blk = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(s_addr + c * 32, r);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int t = 0; t < 32; t += 2) {
+                    const int kk = k0 + c * 32 + t;
+                    const float p0 = kk < k_lim ? exp2f(__uint_as_float(r[t]) * ap.scale_log2 - m_use) : 0.0f;
+                    const float p1 = kk + 1 < k_lim ? exp2f(__uint_as_float(r[t + 1]) * ap.scale_log2 - m_use) : 0.0f;
+                    l_blk += p0 + p1;
+                    packed[t / 2] = E::pack(p0, p1);
+                }
+                // columns c*32 .. c*32+31 of row `row`: slab = c/2, 16-byte chunks (c%2)*4 .. +3, XOR-swizzled by row%8
+                const uint32_t base = sP + (c / 2) * HALF_BYTES + row * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const uint32_t chunk = static_cast<uint32_t>(((c & 1) * 4 + q4) ^ (row & 7));
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + chunk * 16), "r"(packed[q4 * 4 + 0]), "r"(packed[q4 * 4 + 1]),
+                                 "r"(packed[q4 * 4 + 2]), "r"(packed[q4 * 4 + 3]) : "memory");
+                }
+            }
+            l_run = l_run * alpha + l_blk;
+            m_run = m_new;
+            fence_proxy_async();   // P (generic-proxy stores) must be visible to the tensor core's reads
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(s_empty + 8 * (j & 1)); mbar_arrive(p_full); }
+        }
+        // epilogue: O / l -> 16-bit -> global
+        if (ok && mbar_wait(pv_done, (nblk - 1) & 1, status, 0x2b)) {
+            tc_fence_after();
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            T* orow = reinterpret_cast<T*>(ap.out) + (static_cast<size_t>(bh) * ap.seq + qi) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(lane_addr + O_COL + c * 32, r);
+                tmem_ld_wait();
+                if (qi < ap.seq) {
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 u;
+                        u.x = E::pack(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv);
+                        u.y = E::pack(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv);
+                        u.z = E::pack(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv);
+                        u.w = E::pack(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv);
+                        dst[q4] = u;
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*reinterpret_cast<volatile int*>(status) != ST_OK) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// Any-shape path (fp32, head sizes other than 64/128, unaligned pointers): one warp per
+// query row, online softmax over the keys, lanes split the head dimension.
+__device__ __forceinline__ float ald(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float ald(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float ald(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ void ast(float* p, float v) { *p = v; }
+__device__ __forceinline__ void ast(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void ast(__half* p, float v) { *p = __float2half_rn(v); }
+
+template <typename T, int MAXD>
+__global__ void __launch_bounds__(128)
+attention_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V, T* __restrict__ O,
+                         int batch_heads, int seq, int d, float scale, int causal) {
+    constexpr int PER = MAXD / 32;
+    const int lane = threadIdx.x & 31;
+    const size_t rows = static_cast<size_t>(batch_heads) * seq;
+    for (size_t gr = blockIdx.x * 4 + (threadIdx.x >> 5); gr < rows; gr += static_cast<size_t>(gridDim.x) * 4) {
+        const size_t bh = gr / seq;
+        const int i = static_cast<int>(gr % seq);
+        const T* q = Q + gr * d; const T* kb = K + bh * seq * d; const T* vb = V + bh * seq * d;
+        float qv[PER], acc[PER];
+#pragma unroll
+        for (int t = 0; t < PER; ++t) { const int c = lane + 32 * t; qv[t] = c < d ? ald(q + c) * scale : 0.0f; acc[t] = 0.0f; }
+        float m = -INFINITY, l = 0.0f;
+        const int lim = causal ? i + 1 : seq;
+        for (int j = 0; j < lim; ++j) {
+            float s = 0.0f;
+#pragma unroll
+            for (int t = 0; t < PER; ++t) { const int c = lane + 32 * t; if (c < d) s = fmaf(qv[t], ald(kb + static_cast<size_t>(j) * d + c), s); }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            const float mn = fmaxf(m, s), a = expf(m - mn), p = expf(s - mn);
+            l = l * a + p;
+#pragma unroll
+            for (int t = 0; t < PER; ++t) { const int c = lane + 32 * t; if (c < d) acc[t] = acc[t] * a + p * ald(vb + static_cast<size_t>(j) * d + c); }
+            m = mn;
+        }
+#pragma unroll
+        for (int t = 0; t < PER; ++t) { const int c = lane + 32 * t; if (c < d) ast(O + gr * d + c, acc[t] / l); }
+    }
+}
+
+template <typename T>
+int launch_rowwarp(const void* q, const void* k, const void* v, void* o, int bh, int seq, int d, float scale, int causal, cudaStream_t s) {
+    const size_t rows = static_cast<size_t>(bh) * seq;
+    size_t blocks = (rows + 3) / 4;
+    const size_t cap = static_cast<size_t>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    if (d <= 128) attention_rowwarp_kernel<T, 128><<<static_cast<unsigned>(blocks), 128, 0, s>>>(static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), static_cast<T*>(o), bh, seq, d, scale, causal);
+    else if (d <= 512) attention_rowwarp_kernel<T, 512><<<static_cast<unsigned>(blocks), 128, 0, s>>>(static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), static_cast<T*>(o), bh, seq, d, scale, causal);
+    else { set_error("attention: d_head %d > 512 is not supported", d); return -1; }
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+template <int HD, int FMT>
+int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void* k, const void* v, void* out, float scale, int causal,
+                        cudaStream_t stream, int* status) {
+    auto kernel = attention_tc_kernel<HD, FMT>;
+    // At least 120 KB so that two CTAs never share an SM: each one takes all 512 TMEM columns.
+    constexpr size_t smem = AttnSmem<HD>::BYTES > 120 * 1024 ? AttnSmem<HD>::BYTES : 120 * 1024;
+    static bool attr_set[16] = {};
+    int dev = 0;
+    B200_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 16 && !attr_set[dev]) {
+        B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        attr_set[dev] = true;
+    }
+    CUtensorMap tq, tk, tv;
+    const uint64_t dims[3] = {static_cast<uint64_t>(HD), static_cast<uint64_t>(seq), static_cast<uint64_t>(bh)};
+    const uint64_t str[2] = {static_cast<uint64_t>(HD) * 2, static_cast<uint64_t>(seq) * HD * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    if (encode_tmap(&tq, q, 2, 3, dims, str, box, true) != 0 || encode_tmap(&tk, k, 2, 3, dims, str, box, true) != 0 ||
+        encode_tmap(&tv, v, 2, 3, dims, str, box, true) != 0) return -1;
+    AttnParams ap;
+    ap.seq = seq; ap.batch_heads = bh; ap.causal = causal ? 1 : 0; ap.scale_log2 = scale * 1.4426950408889634f; ap.out = out;
+    dim3 grid((seq + BQ - 1) / BQ, bh);
+    kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+}  // namespace
+
+int launch_attention(pyc_dtype dt, int batch_heads, int seq, int d, const void* q, const void* k, const void* v, void* out, float scale,
+                     int causal, cudaStream_t s, int* status) {
+    if (batch_heads <= 0 || seq <= 0 || d <= 0 || !q || !k || !v || !out) { set_error("attention: bad shape or NULL pointer"); return -1; }
+    auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool tc = (dt == PYC_DTYPE_BF16 || dt == PYC_DTYPE_F16) && (d == 64 || d == 128) && scale > 0.0f && status && batch_heads <= 65535 &&
+                    aligned(q) && aligned(k) && aligned(v) && aligned(out);
+    if (tc) {
+        const bool bf = dt == PYC_DTYPE_BF16;
+        if (d == 128) return bf ? launch_attention_tc<128, 1>(dt, batch_heads, seq, q, k, v, out, scale, causal, s, status)
+                                : launch_attention_tc<128, 0>(dt, batch_heads, seq, q, k, v, out, scale, causal, s, status);
+        return bf ? launch_attention_tc<64, 1>(dt, batch_heads, seq, q, k, v, out, scale, causal, s, status)
+                  : launch_attention_tc<64, 0>(dt, batch_heads, seq, q, k, v, out, scale, causal, s, status);
+    }
+    switch (dt) {
+        case PYC_DTYPE_F32: return launch_rowwarp<float>(q, k, v, out, batch_heads, seq, d, scale, causal, s);
+        case PYC_DTYPE_BF16: return launch_rowwarp<__nv_bfloat16>(q, k, v, out, batch_heads, seq, d, scale, causal, s);
+        case PYC_DTYPE_F16: return launch_rowwarp<__half>(q, k, v, out, batch_heads, seq, d, scale, causal, s);
+        default: set_error("attention: unsupported dtype %d", static_cast<int>(dt)); return -1;
+    }
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int pyc_b200_attention(pyc_dtype dtype, int batch_heads, int seq_len, int d_head, const void* Q, const void* K, const void* V, void* Out,
+                       float scale, int causal, void* stream) {
+    return b200::launch_attention(dtype, batch_heads, seq_len, d_head, Q, K, V, Out, scale, causal, static_cast<cudaStream_t>(stream),
+                                  b200::device_status_word());
+}
+
+int pyc_cutlass_attention_dispatch(const char* symbol, int seq_len, int d_head, const void* Q, const void* K, const void* V, void* Out,
+                                   float scale, void* stream) {
+    if (!symbol) return -1;
+    pyc_dtype dt; int causal = 0;
+    if (!strcmp(symbol, "b200_attention_bf16") || !strcmp(symbol, "cutlass_attention_bf16")) dt = PYC_DTYPE_BF16;
+    else if (!strcmp(symbol, "b200_attention_f16") || !strcmp(symbol, "cutlass_attention_f16")) dt = PYC_DTYPE_F16;
+    else if (!strcmp(symbol, "b200_attention_bf16_causal")) { dt = PYC_DTYPE_BF16; causal = 1; }
+    else if (!strcmp(symbol, "b200_attention_f16_causal")) { dt = PYC_DTYPE_F16; causal = 1; }
+    else if (!strcmp(symbol, "b200_attention_f32")) dt = PYC_DTYPE_F32;
+    else { b200::set_error("unknown attention symbol %s", symbol); return -1; }
+    return pyc_b200_attention(dt, 1, seq_len, d_head, Q, K, V, Out, scale, causal, stream);
+}
+
+}  // extern "C"
