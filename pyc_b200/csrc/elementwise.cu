@@ -13,6 +13,7 @@
 #include <cuda_fp16.h>
 
 #include "internal.h"
+#include "math.cuh"
 
 namespace b200 {
 namespace {
@@ -55,7 +56,7 @@ __device__ __forceinline__ void store_vec(T* p, const float (&f)[VEC]) {
 
 __device__ __forceinline__ float act_fn(float v, int act) {
     if (act == PYC_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
-    if (act == PYC_B200_ACT_GELU) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    if (act == PYC_B200_ACT_GELU) return gelu_erf(v);
     return v;
 }
 
@@ -127,14 +128,37 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return v;
 }
 
-// One row per group of THREADS threads (THREADS = 32: several rows per CTA).
-// Each thread owns up to VPT vectors of its row in registers; CACHED == false is
-// the any-width form that re-reads the row from global memory instead.
+// Raw storage of one vector access: the row stays in registers between passes as packed
+// 16-byte words (4 registers per 8 bf16), not as widened floats, which keeps occupancy up.
+template <typename T, int VEC> struct RawVec { uint4 u; };
+template <typename T> struct RawVec<T, 1> { T u; };
+template <typename T, int VEC>
+__device__ __forceinline__ RawVec<T, VEC> load_raw(const T* p) {
+    RawVec<T, VEC> r;
+    if constexpr (VEC == 1) r.u = *p; else r.u = __ldg(reinterpret_cast<const uint4*>(p));
+    return r;
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void widen(const RawVec<T, VEC>& r, float (&f)[VEC]) {
+    if constexpr (VEC == 1) {
+        f[0] = to_f(r.u);
+    } else {
+        union { uint4 u; T t[VEC]; } x;
+        x.u = r.u;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) f[i] = to_f(x.t[i]);
+    }
+}
+
+// One row per group of THREADS threads (THREADS = 32: four rows per CTA).  Each thread
+// owns up to VPT vectors of its row in registers; CACHED == false is the any-width form
+// that re-reads the row from global memory instead.
 template <typename T, int VEC, int THREADS, int VPT, bool CACHED, int OP>
-__global__ void __launch_bounds__(THREADS >= 128 ? THREADS : 128)
+__global__ void __launch_bounds__(THREADS >= 128 ? THREADS : 128, THREADS >= 256 ? 4 : 8)
 row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
            size_t rows, size_t cols, float eps) {
     constexpr int ROWS_PER_CTA = THREADS >= 128 ? 1 : 128 / THREADS;
+    constexpr int NV = CACHED ? VPT : 1;
     __shared__ float scratch[8];
     const int tid = THREADS >= 128 ? threadIdx.x : (threadIdx.x % THREADS);
     const size_t nvec = cols / VEC;
@@ -142,106 +166,85 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
          row < rows; row += static_cast<size_t>(gridDim.x) * ROWS_PER_CTA) {
         const T* xr = x + row * cols;
         T* orow = out + (OP == ROW_SUM ? 0 : row * cols);
-        float v[CACHED ? VPT : 1][VEC];
-        float s = 0.0f, mx = -INFINITY;
+        RawVec<T, VEC> raw[NV];
+        // Visit every vector this thread owns: from registers when cached, else from global memory.
+        auto for_each = [&](auto&& fn) {
+            if constexpr (CACHED) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const size_t vi = tid + static_cast<size_t>(i) * THREADS;
+                    if (vi < nvec) { float f[VEC]; widen<T, VEC>(raw[i], f); fn(f, vi); }
+                }
+            } else {
+                for (size_t vi = tid; vi < nvec; vi += THREADS) { float f[VEC]; widen<T, VEC>(load_raw<T, VEC>(xr + vi * VEC), f); fn(f, vi); }
+            }
+        };
         if constexpr (CACHED) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const size_t vi = tid + static_cast<size_t>(i) * THREADS;
-                if (vi < nvec) {
-                    load_vec<T, VEC>(xr + vi * VEC, v[i]);
-#pragma unroll
-                    for (int j = 0; j < VEC; ++j) { s += v[i][j]; mx = fmaxf(mx, v[i][j]); }
-                }
-            }
-        } else {
-            for (size_t vi = tid; vi < nvec; vi += THREADS) {
-                load_vec<T, VEC>(xr + vi * VEC, v[0]);
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) { s += v[0][j]; mx = fmaxf(mx, v[0][j]); }
+                if (vi < nvec) raw[i] = load_raw<T, VEC>(xr + vi * VEC);
             }
         }
         if constexpr (OP == ROW_SUM) {
+            float s = 0.0f;
+            for_each([&](float (&f)[VEC], size_t) {
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) s += f[j];
+            });
             s = block_sum<THREADS>(s, scratch);
             if (tid == 0) from_f(out[row], s);
         } else if constexpr (OP == ROW_LAYERNORM) {
+            float s = 0.0f;
+            for_each([&](float (&f)[VEC], size_t) {
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) s += f[j];
+            });
             const float mean = block_sum<THREADS>(s, scratch) / static_cast<float>(cols);
             float ss = 0.0f;
-            if constexpr (CACHED) {
+            for_each([&](float (&f)[VEC], size_t) {
 #pragma unroll
-                for (int i = 0; i < VPT; ++i)
-                    if (tid + static_cast<size_t>(i) * THREADS < nvec)
-#pragma unroll
-                        for (int j = 0; j < VEC; ++j) { const float d = v[i][j] - mean; ss += d * d; }
-            } else {
-                for (size_t vi = tid; vi < nvec; vi += THREADS) {
-                    load_vec<T, VEC>(xr + vi * VEC, v[0]);
-#pragma unroll
-                    for (int j = 0; j < VEC; ++j) { const float d = v[0][j] - mean; ss += d * d; }
-                }
-            }
+                for (int j = 0; j < VEC; ++j) { const float d = f[j] - mean; ss = fmaf(d, d, ss); }
+            });
             const float rstd = rsqrtf(block_sum<THREADS>(ss, scratch) / static_cast<float>(cols) + eps);
-            auto finish = [&](float (&val)[VEC], size_t vi) {
+            for_each([&](float (&f)[VEC], size_t vi) {
                 float g[VEC], b[VEC];
                 if (gamma) load_vec<T, VEC>(gamma + vi * VEC, g);
                 if (beta) load_vec<T, VEC>(beta + vi * VEC, b);
 #pragma unroll
                 for (int j = 0; j < VEC; ++j) {
-                    float y = (val[j] - mean) * rstd;
+                    float y = (f[j] - mean) * rstd;
                     if (gamma) y *= g[j];
                     if (beta) y += b[j];
-                    val[j] = y;
+                    f[j] = y;
                 }
-                store_vec<T, VEC>(orow + vi * VEC, val);
-            };
-            if constexpr (CACHED) {
-#pragma unroll
-                for (int i = 0; i < VPT; ++i) { const size_t vi = tid + static_cast<size_t>(i) * THREADS; if (vi < nvec) finish(v[i], vi); }
-            } else {
-                for (size_t vi = tid; vi < nvec; vi += THREADS) { load_vec<T, VEC>(xr + vi * VEC, v[0]); finish(v[0], vi); }
-            }
+                store_vec<T, VEC>(orow + vi * VEC, f);
+            });
         } else {  // softmax
+            float mx = -INFINITY;
+            for_each([&](float (&f)[VEC], size_t) {
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) mx = fmaxf(mx, f[j]);
+            });
             mx = block_max<THREADS>(mx, scratch);
             float den = 0.0f;
-            if constexpr (CACHED) {
+            for_each([&](float (&f)[VEC], size_t) {
 #pragma unroll
-                for (int i = 0; i < VPT; ++i)
-                    if (tid + static_cast<size_t>(i) * THREADS < nvec)
-#pragma unroll
-                        for (int j = 0; j < VEC; ++j) { v[i][j] = __expf(v[i][j] - mx); den += v[i][j]; }
-            } else {
-                for (size_t vi = tid; vi < nvec; vi += THREADS) {
-                    load_vec<T, VEC>(xr + vi * VEC, v[0]);
-#pragma unroll
-                    for (int j = 0; j < VEC; ++j) den += __expf(v[0][j] - mx);
-                }
-            }
+                for (int j = 0; j < VEC; ++j) den += expf(f[j] - mx);
+            });
             const float inv = 1.0f / block_sum<THREADS>(den, scratch);
-            if constexpr (CACHED) {
+            for_each([&](float (&f)[VEC], size_t vi) {
 #pragma unroll
-                for (int i = 0; i < VPT; ++i) {
-                    const size_t vi = tid + static_cast<size_t>(i) * THREADS;
-                    if (vi < nvec) {
-#pragma unroll
-                        for (int j = 0; j < VEC; ++j) v[i][j] *= inv;
-                        store_vec<T, VEC>(orow + vi * VEC, v[i]);
-                    }
-                }
-            } else {
-                for (size_t vi = tid; vi < nvec; vi += THREADS) {
-                    load_vec<T, VEC>(xr + vi * VEC, v[0]);
-#pragma unroll
-                    for (int j = 0; j < VEC; ++j) v[0][j] = __expf(v[0][j] - mx) * inv;
-                    store_vec<T, VEC>(orow + vi * VEC, v[0]);
-                }
-            }
+                for (int j = 0; j < VEC; ++j) f[j] = expf(f[j] - mx) * inv;
+                store_vec<T, VEC>(orow + vi * VEC, f);
+            });
         }
     }
 }
 
 inline int flat_grid(size_t work_items, int threads) {
     const size_t blocks = (work_items + threads - 1) / threads;
-    const size_t cap = static_cast<size_t>(sm_count()) * 16;  // 16 resident CTAs of 256 threads would oversubscribe: 8 fit
+    const size_t cap = static_cast<size_t>(sm_count()) * 8;  // 8 CTAs of 256 threads fill an SM's 2048 thread slots
     return static_cast<int>(blocks < cap ? (blocks ? blocks : 1) : cap);
 }
 

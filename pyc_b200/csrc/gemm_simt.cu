@@ -13,6 +13,7 @@
 #include <cuda_fp16.h>
 
 #include "internal.h"
+#include "math.cuh"
 
 namespace b200 {
 namespace {
@@ -28,7 +29,7 @@ __device__ __forceinline__ void stf(__half* p, float v) { *p = __float2half_rn(v
 
 __device__ __forceinline__ float act_fn(float v, int act) {
     if (act == PYC_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
-    if (act == PYC_B200_ACT_GELU) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    if (act == PYC_B200_ACT_GELU) return gelu_erf(v);
     return v;
 }
 

@@ -26,6 +26,7 @@
 #include <mutex>
 
 #include "internal.h"
+#include "math.cuh"
 #include "ptx_sm100.cuh"
 
 namespace b200 {
@@ -46,7 +47,7 @@ struct Epilogue {
 
 __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == PYC_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
-    if (act == PYC_B200_ACT_GELU) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    if (act == PYC_B200_ACT_GELU) return gelu_erf(v);
     return v;
 }
 
