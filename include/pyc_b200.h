@@ -170,6 +170,41 @@ int pyc_b200_conv2d(pyc_dtype dtype, int N, int H, int W, int C_in, int K, int R
                     const void* input, const void* filter, const void* bias, int relu,
                     void* output, void* stream);
 
+/* ---- fp8 (e4m3) weight path: the transformer-FFN configuration ------------ *
+ * No counterpart in PyC (its dtype enum has no fp8).                          */
+
+/* Per-token quantisation of bf16 rows: q = round_e4m3(x / scale), scale[row] = amax(row) / 448
+ * (cols % 8 == 0, cols <= 16384).  The second form applies LayerNorm (last axis, eps, optional
+ * gamma/beta [cols] bf16) first, in the same pass over the row. */
+int pyc_b200_quantize_rows(const void* x_bf16, void* q_e4m3, float* row_scale, size_t rows, size_t cols, void* stream);
+int pyc_b200_layernorm_quantize(const void* x_bf16, const void* gamma, const void* beta, void* q_e4m3, float* row_scale,
+                                size_t rows, size_t cols, float eps, void* stream);
+
+/* D[M,N] (bf16) = act(acc * row_scale[m] * col_scale[n] + bias[n]); A [M,K] e4m3, B [K,N] e4m3 row-major
+ * (or [N,K] when b_col_major); scales and bias may be NULL.  K % 16 == 0, N % 16 == 0. */
+int pyc_b200_gemm_fp8(int M, int N, int K, const void* A_e4m3, const void* B_e4m3, int b_col_major, const float* row_scale,
+                      const float* col_scale, const void* bias_bf16, pyc_b200_activation act, void* D_bf16, void* stream);
+
+/* One FFN block: out = W2^T-form( GELU( LN(x) * W1 + b1 ) ) * ... i.e.
+ *   out[T,H] = (gelu(layernorm(x)[T,H] . W1[H,I] + b1[I]) . W2[I,H]) + b2[H]
+ * x, out, biases bf16; W1, W2 e4m3 row-major with one fp32 scale per OUTPUT channel (w1_scale[I], w2_scale[H]);
+ * activations are quantised per token to e4m3 in front of each GEMM, both GEMMs run on the fp8 tensor-core path.
+ * Tensor parallel use: give each rank its column slice of W1 / b1 / w1_scale and row slice of W2 (inner = I / ranks),
+ * b2 on one rank only; `out` is then a partial sum to be all-reduced by the caller.
+ * The caller provides the scratch: pyc_b200_ffn_workspace_bytes(tokens, hidden, inner) bytes, 256-byte aligned. */
+typedef struct {
+    int tokens, hidden, inner;
+    const void* x;
+    const void* ln_gamma;   /* may be NULL */
+    const void* ln_beta;    /* may be NULL */
+    float eps;              /* <= 0: 1e-5 */
+    const void* w1; const float* w1_scale; const void* b1;   /* b1 may be NULL */
+    const void* w2; const float* w2_scale; const void* b2;   /* b2 may be NULL */
+    void* out;
+} pyc_b200_ffn_args;
+size_t pyc_b200_ffn_workspace_bytes(int tokens, int hidden, int inner);
+int pyc_b200_ffn_block(const pyc_b200_ffn_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Time every registered tile configuration for (dtype, M, N, K) with CUDA
  * events, feed the measured milliseconds to PyC's registry
  * (pyc_kernel_benchmark_update_symbol) when it is linked, remember the winner

@@ -254,3 +254,16 @@ class RefRuntime:
 
 def ref_cpu(threads=None):
     return RefRuntime(REF_CPU_SO, threads)
+
+
+def ffn_reference(orc, x, w1_codes, s1, w2_codes, s2, b1=None, b2=None, eps=1e-5):
+    """CPU definition of the FFN block (UNPINNED: PyC has neither fp8 nor an FFN op): fp32 throughout on the given
+    bf16-rounded x and the DEQUANTISED fp8 weights; the contractions are the oracle's matmul (PyC's summation order)."""
+    from pyc_b200 import workloads
+    w1 = workloads.e4m3_decode(w1_codes) * np.asarray(s1, np.float32)[None, :]
+    w2 = workloads.e4m3_decode(w2_codes) * np.asarray(s2, np.float32)[None, :]
+    h = orc.matmul(orc.layernorm(x, eps=eps), w1)
+    if b1 is not None:
+        h = orc.add(h, b1)
+    y = orc.matmul(orc.gelu(h), w2)
+    return orc.add(y, b2) if b2 is not None else y

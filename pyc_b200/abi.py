@@ -84,6 +84,12 @@ class GemmArgs(C.Structure):
                 ("alpha", C.c_float), ("add_mode", C.c_int), ("add", C.c_void_p), ("act", C.c_int)]
 
 
+class FfnArgs(C.Structure):
+    _fields_ = [("tokens", C.c_int), ("hidden", C.c_int), ("inner", C.c_int), ("x", C.c_void_p), ("ln_gamma", C.c_void_p),
+                ("ln_beta", C.c_void_p), ("eps", C.c_float), ("w1", C.c_void_p), ("w1_scale", C.c_void_p), ("b1", C.c_void_p),
+                ("w2", C.c_void_p), ("w2_scale", C.c_void_p), ("b2", C.c_void_p), ("out", C.c_void_p)]
+
+
 class RuntimeInfo(C.Structure):
     _fields_ = [("arena_bytes", C.c_size_t), ("plan_peak_bytes", C.c_size_t), ("plan_total_bytes", C.c_size_t),
                 ("graphs_cached", C.c_size_t), ("graph_replays", C.c_size_t), ("kernels_per_graph", C.c_size_t),

@@ -20,7 +20,8 @@ EXPORTS = [
     "pyc_cutlass_kernel_count", "pyc_cutlass_registry_init",
     # additive
     "pyc_b200_gemm", "pyc_b200_gemm_static", "pyc_b200_add", "pyc_b200_bias_act", "pyc_b200_layernorm", "pyc_b200_softmax",
-    "pyc_b200_reduce_sum", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm",
+    "pyc_b200_reduce_sum", "pyc_b200_quantize_rows", "pyc_b200_layernorm_quantize", "pyc_b200_gemm_fp8",
+    "pyc_b200_ffn_workspace_bytes", "pyc_b200_ffn_block", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm",
     "pyc_b200_get_runtime_info", "pyc_b200_set_stream", "pyc_b200_device_status", "pyc_b200_last_error",
     "pyc_b200_shutdown",
 ]
@@ -59,6 +60,12 @@ def load():
     L.pyc_b200_layernorm.argtypes = [i, vp, vp, vp, vp, sz, sz, f, vp]
     L.pyc_b200_softmax.argtypes = [i, vp, vp, sz, sz, vp]
     L.pyc_b200_reduce_sum.argtypes = [i, vp, vp, sz, sz, vp]
+    L.pyc_b200_quantize_rows.argtypes = [vp, vp, vp, sz, sz, vp]
+    L.pyc_b200_layernorm_quantize.argtypes = [vp, vp, vp, vp, vp, sz, sz, f, vp]
+    L.pyc_b200_gemm_fp8.argtypes = [i, i, i, vp, vp, i, vp, vp, vp, i, vp, vp]
+    L.pyc_b200_ffn_workspace_bytes.argtypes = [i, i, i]
+    L.pyc_b200_ffn_workspace_bytes.restype = sz
+    L.pyc_b200_ffn_block.argtypes = [C.POINTER(abi.FfnArgs), vp, sz, vp]
     L.pyc_b200_attention.argtypes = [i, i, i, i, vp, vp, vp, vp, f, i, vp]
     L.pyc_b200_conv2d.argtypes = [i] * 12 + [vp, vp, vp, i, vp, vp]
     L.pyc_b200_autotune_gemm.argtypes = [i, i, i, i, i, C.c_char_p, sz, C.POINTER(C.c_double)]
@@ -159,6 +166,33 @@ def softmax(dtype, x, out, rows, cols, stream=0):
 
 def reduce_sum(dtype, x, out, rows, cols, stream=0):
     _check(load().pyc_b200_reduce_sum(dtype, x, out, rows, cols, stream), "pyc_b200_reduce_sum")
+
+
+def quantize_rows(x, q, scale, rows, cols, stream=0):
+    _check(load().pyc_b200_quantize_rows(x, q, scale, rows, cols, stream), "pyc_b200_quantize_rows")
+
+
+def layernorm_quantize(x, gamma, beta, q, scale, rows, cols, eps=1e-5, stream=0):
+    _check(load().pyc_b200_layernorm_quantize(x, gamma, beta, q, scale, rows, cols, eps, stream), "pyc_b200_layernorm_quantize")
+
+
+def gemm_fp8(M, N, K, A, B, D, row_scale=None, col_scale=None, bias=None, act=abi.ACT_NONE, b_col_major=False, stream=0):
+    _check(load().pyc_b200_gemm_fp8(M, N, K, A, B, int(b_col_major), row_scale, col_scale, bias, act, D, stream), "pyc_b200_gemm_fp8")
+
+
+def ffn_workspace_bytes(tokens, hidden, inner):
+    return int(load().pyc_b200_ffn_workspace_bytes(tokens, hidden, inner))
+
+
+def ffn_block(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, out, workspace, workspace_bytes,
+              ln_gamma=None, ln_beta=None, b1=None, b2=None, eps=1e-5, stream=0):
+    a = abi.FfnArgs()
+    a.tokens, a.hidden, a.inner = tokens, hidden, inner
+    a.x, a.ln_gamma, a.ln_beta, a.eps = x, ln_gamma, ln_beta, eps
+    a.w1, a.w1_scale, a.b1 = w1, w1_scale, b1
+    a.w2, a.w2_scale, a.b2 = w2, w2_scale, b2
+    a.out = out
+    _check(load().pyc_b200_ffn_block(C.byref(a), workspace, workspace_bytes, stream), "pyc_b200_ffn_block")
 
 
 def attention(dtype, batch_heads, seq, d, q, k, v, out, scale, causal, stream=0):

@@ -1,0 +1,237 @@
+// fp8 (e4m3) x fp8 (e4m3) GEMM on the tcgen05 tensor cores (kind::f8f6f4), fp32
+// accumulation in TMEM, with dequantisation fused into the epilogue:
+//     D[m,n] = act( acc[m,n] * row_scale[m] * col_scale[n] + bias[n] )   -> bf16
+// row_scale is the per-token scale of the quantised activations, col_scale the
+// per-output-channel scale of the quantised weights.
+//
+// PyC has no fp8 dtype or kernel (include/pyc/ir.h:16-23 stops at I8); this is the
+// weight path of the transformer-FFN benchmark configuration, reached through the
+// additive entry points only.  Structure identical to gemm_tc.cu (persistent CTA,
+// TMA ring, single-thread MMA issuer, double-buffered TMEM accumulators, four
+// epilogue warps); what changes is the element size: a 128-byte swizzle row holds
+// 128 k-values, one MMA consumes K = 32, B stored [K,N] row-major is the MN-major
+// operand with 128-column slabs (LBO = 16 KB, SBO = 1 KB).
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "internal.h"
+#include "math.cuh"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 128;                      // fp8 elements per stage row = 128 bytes
+constexpr int A_STAGE_BYTES = BM * BK;
+constexpr int GROUP_M = 16;
+
+struct Fp8Epilogue {
+    __nv_bfloat16* D;
+    const float* row_scale;   // [M] or null
+    const float* col_scale;   // [N] or null
+    const __nv_bfloat16* bias;  // [N] or null
+    int act;
+};
+
+__device__ __forceinline__ void fp8_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int group = GROUP_M * tiles_n;
+    const int g = tile / group;
+    const int first = g * GROUP_M;
+    const int gm = min(GROUP_M, tiles_m - first);
+    const int local = tile - g * group;
+    tm = first + local % gm;
+    tn = local / gm;
+}
+
+template <int BN, int STAGES, bool B_KMAJOR>
+__global__ void __launch_bounds__(192, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Fp8Epilogue ep, int M, int N, int K, int* status) {
+    constexpr int B_STAGE_BYTES = BN * BK;
+    constexpr uint32_t STAGE_TX = A_STAGE_BYTES + B_STAGE_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr uint32_t IDESC = make_idesc(0, 0, 0, B_KMAJOR ? 0 : 1, BM, BN);  // e4m3 x e4m3 -> f32
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int tm, tn;
+                fp8_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                const int m0 = tm * BM, n0 = tn * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, status, 0x31)) { ok = false; break; }
+                    const uint32_t fb = full0 + 8 * stage;
+                    mbar_arrive_expect_tx(fb, STAGE_TX);
+                    tma_load_2d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, fb, kb * BK, m0);
+                    const uint32_t bdst = smem_u32(sB + stage * B_STAGE_BYTES);
+                    if (B_KMAJOR) {
+                        tma_load_2d(bdst, &tmB, fb, kb * BK, n0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 128; ++j) tma_load_2d(bdst + j * (BK * 128), &tmB, fb, n0 + j * 128, kb * BK);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, status, 0x32)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8 * stage, phase, status, 0x33)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES), b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+                    for (int k4 = 0; k4 < BK / 32; ++k4) {  // one MMA = 32 k-values = 32 bytes of a K-major row
+                        const uint64_t adesc = make_smem_desc_sw128(a_base + k4 * 32, 16, 1024);
+                        const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_base + k4 * 32, 16, 1024)
+                                                        : make_smem_desc_sw128(b_base + k4 * (32 * 128), BK * 128, 1024);
+                        umma_f8(d_tmem, adesc, bdesc, IDESC, (kb | k4) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(tfull0 + 8 * acc);
+            }
+        }
+    } else {
+        const int wq = warp & 3;
+        int it = 0;
+        const bool vec_ok = (N % 8 == 0) && (reinterpret_cast<uintptr_t>(ep.D) % 16 == 0);
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            int tm, tn;
+            fp8_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int row = tm * BM + wq * 32 + lane;
+            const int n0 = tn * BN;
+            if (!mbar_wait(tfull0 + 8 * acc, acc_phase, status, 0x34)) break;
+            tc_fence_after();
+            const float rs = (ep.row_scale && row < M) ? ep.row_scale[row] : 1.0f;
+            __nv_bfloat16* drow = ep.D + static_cast<size_t>(row) * N;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * BN + c * 32, r);
+                tmem_ld_wait();
+                const int col0 = n0 + c * 32;  // warp-uniform
+                if (col0 < N && row < M) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = col0 + j;
+                        float x = __uint_as_float(r[j]) * rs;
+                        if (col < N) {
+                            if (ep.col_scale) x *= __ldg(ep.col_scale + col);
+                            if (ep.bias) x += __bfloat162float(ep.bias[col]);
+                        }
+                        v[j] = apply_activation(x, ep.act);
+                    }
+                    if (vec_ok && col0 + 32 <= N) {
+                        uint4* dst = reinterpret_cast<uint4*>(drow + col0);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]), p1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]), p3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
+                            uint4 u;
+                            u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
+                            u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
+                            dst[q] = u;
+                        }
+                    } else {
+                        for (int j = 0; j < 32; ++j) if (col0 + j < N) drow[col0 + j] = __float2bfloat16_rn(v[j]);
+                    }
+                }
+                __syncwarp();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*reinterpret_cast<volatile int*>(status) != ST_OK) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int BN, int STAGES, bool B_KMAJOR>
+int launch_fp8_instance(int M, int N, int K, const void* A, const void* B, const Fp8Epilogue& ep, cudaStream_t stream, int* status) {
+    auto kernel = gemm_fp8_kernel<BN, STAGES, B_KMAJOR>;
+    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + BN * BK) + (2 * STAGES + 4) * 8 + 16;
+    static bool attr_set[16] = {};
+    int dev = 0;
+    B200_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 16 && !attr_set[dev]) {
+        B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        attr_set[dev] = true;
+    }
+    CUtensorMap tmA, tmB;
+    if (encode_tmap_2d(&tmA, A, 1, M, K, static_cast<uint64_t>(K), BM, BK) != 0) return -1;
+    if (B_KMAJOR) { if (encode_tmap_2d(&tmB, B, 1, N, K, static_cast<uint64_t>(K), BN, BK) != 0) return -1; }
+    else { if (encode_tmap_2d(&tmB, B, 1, K, N, static_cast<uint64_t>(N), BK, 128) != 0) return -1; }
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    kernel<<<tiles < sm_count() ? tiles : sm_count(), 192, smem, stream>>>(tmA, tmB, ep, M, N, K, status);
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+}  // namespace
+
+int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col_major, const float* row_scale, const float* col_scale,
+                    const void* bias, int act, void* D, cudaStream_t stream, int* status) {
+    if (M <= 0 || N <= 0 || K <= 0 || !A || !B || !D || !status) { set_error("fp8 gemm: bad shape or NULL pointer"); return -1; }
+    if (K % 16 != 0 || (!b_col_major && N % 16 != 0) || reinterpret_cast<uintptr_t>(A) % 16 || reinterpret_cast<uintptr_t>(B) % 16) {
+        set_error("fp8 gemm: needs K %% 16 == 0, N %% 16 == 0 for row-major B and 16-byte aligned operands (TMA)"); return -1;
+    }
+    Fp8Epilogue ep;
+    ep.D = static_cast<__nv_bfloat16*>(D); ep.row_scale = row_scale; ep.col_scale = col_scale;
+    ep.bias = static_cast<const __nv_bfloat16*>(bias); ep.act = act;
+    const int sms = sm_count();
+    const long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256), t128 = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
+    const bool use256 = ((t256 + sms - 1) / sms) * 256 <= ((t128 + sms - 1) / sms) * 128 * 1.15;
+    if (use256) return b_col_major ? launch_fp8_instance<256, 4, true>(M, N, K, A, B, ep, stream, status) : launch_fp8_instance<256, 4, false>(M, N, K, A, B, ep, stream, status);
+    return b_col_major ? launch_fp8_instance<128, 6, true>(M, N, K, A, B, ep, stream, status) : launch_fp8_instance<128, 6, false>(M, N, K, A, B, ep, stream, status);
+}
+
+}  // namespace b200

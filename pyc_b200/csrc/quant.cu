@@ -1,0 +1,194 @@
+// Per-token fp8 (e4m3) quantisation of bf16 activations, optionally fused with the
+// LayerNorm in front of it, and the FFN block that strings the fp8 GEMMs together.
+//
+// PyC has no fp8 path; these kernels belong to the transformer-FFN benchmark
+// configuration (LayerNorm -> fp8 GEMM -> GELU -> fp8 GEMM).  Both quantisers are
+// HBM-bound: one CTA per row, the row is read once (kept as packed 16-byte words in
+// registers), scale = amax / 448 per row, values rounded to nearest-even e4m3.
+//   layernorm_quant : x[rows,cols] bf16 -> LN (eps, optional gamma/beta) -> q[rows,cols] e4m3 + scale[rows]
+//   quant_rows      : x[rows,cols] bf16 ->                                 q[rows,cols] e4m3 + scale[rows]
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "internal.h"
+
+namespace b200 {
+int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col_major, const float* row_scale, const float* col_scale,
+                    const void* bias, int act, void* D, cudaStream_t stream, int* status);
+
+namespace {
+
+constexpr int QT = 256;  // threads per row
+
+__device__ __forceinline__ float q_block_reduce(float v, float* scratch, bool is_max) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { const float w = __shfl_xor_sync(0xffffffffu, v, o); v = is_max ? fmaxf(v, w) : v + w; }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();
+    if (l == 0) scratch[w] = v;
+    __syncthreads();
+    v = l < QT / 32 ? scratch[l] : (is_max ? 0.0f : 0.0f);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { const float x = __shfl_xor_sync(0xffffffffu, v, o); v = is_max ? fmaxf(v, x) : v + x; }
+    return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+// VPT vectors of 8 bf16 per thread cached (cols <= QT*8*VPT); cols % 8 == 0.
+template <int VPT, bool LN>
+__global__ void __launch_bounds__(QT, 4)
+rowquant_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
+                uint8_t* __restrict__ q, float* __restrict__ scale, size_t rows, size_t cols, float eps) {
+    __shared__ float scratch[8];
+    const size_t nvec = cols / 8;
+    for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const __nv_bfloat16* xr = x + row * cols;
+        uint4 raw[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const size_t vi = threadIdx.x + static_cast<size_t>(i) * QT;
+            if (vi < nvec) raw[i] = __ldg(reinterpret_cast<const uint4*>(xr) + vi);
+        }
+        float mean = 0.0f, rstd = 1.0f;
+        if constexpr (LN) {
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+                if (threadIdx.x + static_cast<size_t>(i) * QT < nvec) { float f[8]; unpack8(raw[i], f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) s += f[j]; }
+            mean = q_block_reduce(s, scratch, false) / static_cast<float>(cols);
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+                if (threadIdx.x + static_cast<size_t>(i) * QT < nvec) { float f[8]; unpack8(raw[i], f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { const float d = f[j] - mean; ss = fmaf(d, d, ss); } }
+            rstd = rsqrtf(q_block_reduce(ss, scratch, false) / static_cast<float>(cols) + eps);
+        }
+        // value after the optional LayerNorm
+        auto value = [&](const float (&f)[8], size_t vi, float (&y)[8]) {
+            if constexpr (LN) {
+                float g[8], b[8];
+                if (gamma) unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + vi), g);
+                if (beta) unpack8(__ldg(reinterpret_cast<const uint4*>(beta) + vi), b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { float v = (f[j] - mean) * rstd; if (gamma) v *= g[j]; if (beta) v += b[j]; y[j] = v; }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) y[j] = f[j];
+            }
+        };
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const size_t vi = threadIdx.x + static_cast<size_t>(i) * QT;
+            if (vi < nvec) { float f[8], y[8]; unpack8(raw[i], f); value(f, vi, y);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j])); }
+        }
+        amax = q_block_reduce(amax, scratch, true);
+        const float sc = amax > 0.0f ? amax * (1.0f / 448.0f) : 1.0f;
+        const float inv = 1.0f / sc;
+        if (threadIdx.x == 0) scale[row] = sc;
+        uint2* qrow = reinterpret_cast<uint2*>(q + row * cols);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const size_t vi = threadIdx.x + static_cast<size_t>(i) * QT;
+            if (vi < nvec) {
+                float f[8], y[8]; unpack8(raw[i], f); value(f, vi, y);
+                uint2 o;
+                o.x = pack_e4m3x4(y[0] * inv, y[1] * inv, y[2] * inv, y[3] * inv);
+                o.y = pack_e4m3x4(y[4] * inv, y[5] * inv, y[6] * inv, y[7] * inv);
+                qrow[vi] = o;
+            }
+        }
+    }
+}
+
+template <bool LN>
+int launch_rowquant(const void* x, const void* gamma, const void* beta, void* q, float* scale, size_t rows, size_t cols, float eps, cudaStream_t s) {
+    if (rows == 0 || cols == 0 || cols % 8 != 0 || !x || !q || !scale) { set_error("row quantise: needs cols %% 8 == 0 and non-NULL pointers"); return -1; }
+    auto al = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    if (!al(x) || !al(gamma) || !al(beta) || reinterpret_cast<uintptr_t>(q) % 8) { set_error("row quantise: pointers must be 16-byte aligned"); return -1; }
+    const size_t nvec = cols / 8;
+    size_t grid = rows;
+    const size_t cap = static_cast<size_t>(sm_count()) * 32;
+    if (grid > cap) grid = cap;
+    const auto* xb = static_cast<const __nv_bfloat16*>(x); const auto* g = static_cast<const __nv_bfloat16*>(gamma); const auto* b = static_cast<const __nv_bfloat16*>(beta);
+    auto* qq = static_cast<uint8_t*>(q);
+    if (nvec <= QT * 2) rowquant_kernel<2, LN><<<static_cast<unsigned>(grid), QT, 0, s>>>(xb, g, b, qq, scale, rows, cols, eps);
+    else if (nvec <= QT * 4) rowquant_kernel<4, LN><<<static_cast<unsigned>(grid), QT, 0, s>>>(xb, g, b, qq, scale, rows, cols, eps);
+    else if (nvec <= QT * 8) rowquant_kernel<8, LN><<<static_cast<unsigned>(grid), QT, 0, s>>>(xb, g, b, qq, scale, rows, cols, eps);
+    else { set_error("row quantise: rows wider than %d elements are not supported", QT * 8 * 8); return -1; }
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int pyc_b200_quantize_rows(const void* x_bf16, void* q_e4m3, float* row_scale, size_t rows, size_t cols, void* stream) {
+    return launch_rowquant<false>(x_bf16, nullptr, nullptr, q_e4m3, row_scale, rows, cols, 0.0f, static_cast<cudaStream_t>(stream));
+}
+
+int pyc_b200_layernorm_quantize(const void* x_bf16, const void* gamma, const void* beta, void* q_e4m3, float* row_scale,
+                                size_t rows, size_t cols, float eps, void* stream) {
+    return launch_rowquant<true>(x_bf16, gamma, beta, q_e4m3, row_scale, rows, cols, eps, static_cast<cudaStream_t>(stream));
+}
+
+int pyc_b200_gemm_fp8(int M, int N, int K, const void* A_e4m3, const void* B_e4m3, int b_col_major, const float* row_scale,
+                      const float* col_scale, const void* bias_bf16, pyc_b200_activation act, void* D_bf16, void* stream) {
+    return launch_gemm_fp8(M, N, K, A_e4m3, B_e4m3, b_col_major, row_scale, col_scale, bias_bf16, act, D_bf16,
+                           static_cast<cudaStream_t>(stream), device_status_word());
+}
+
+size_t pyc_b200_ffn_workspace_bytes(int tokens, int hidden, int inner) {
+    if (tokens <= 0 || hidden <= 0 || inner <= 0) return 0;
+    const size_t T = tokens, H = hidden, I = inner;
+    return align256(T * H) + align256(T * 4) + align256(T * I * 2) + align256(T * I) + align256(T * 4);
+}
+
+int pyc_b200_ffn_block(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!a || !a->x || !a->w1 || !a->w2 || !a->w1_scale || !a->w2_scale || !a->out || !workspace) { set_error("ffn: NULL argument"); return -1; }
+    const size_t need = pyc_b200_ffn_workspace_bytes(a->tokens, a->hidden, a->inner);
+    if (need == 0 || workspace_bytes < need) { set_error("ffn: workspace of %zu bytes needed, %zu given", need, workspace_bytes); return -1; }
+    if (reinterpret_cast<uintptr_t>(workspace) % 256) { set_error("ffn: workspace must be 256-byte aligned"); return -1; }
+    const size_t T = a->tokens, H = a->hidden, I = a->inner;
+    char* p = static_cast<char*>(workspace);
+    void* xq = p; p += align256(T * H);
+    float* xs = reinterpret_cast<float*>(p); p += align256(T * 4);
+    void* h = p; p += align256(T * I * 2);
+    void* hq = p; p += align256(T * I);
+    float* hs = reinterpret_cast<float*>(p);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int* st = device_status_word();
+    if (!st) return -1;
+    // 1. LayerNorm + per-token quantisation   2. fp8 GEMM1 (+bias) + GELU -> bf16
+    // 3. per-token quantisation               4. fp8 GEMM2 (+bias) -> bf16 (a partial sum when the inner dimension is sharded)
+    if (launch_rowquant<true>(a->x, a->ln_gamma, a->ln_beta, xq, xs, T, H, a->eps > 0.0f ? a->eps : 1e-5f, s) != 0) return -1;
+    if (launch_gemm_fp8(a->tokens, a->inner, a->hidden, xq, a->w1, 0, xs, a->w1_scale, a->b1, PYC_B200_ACT_GELU, h, s, st) != 0) return -1;
+    if (launch_rowquant<false>(h, nullptr, nullptr, hq, hs, T, I, 0.0f, s) != 0) return -1;
+    if (launch_gemm_fp8(a->tokens, a->hidden, a->inner, hq, a->w2, 0, hs, a->w2_scale, a->b2, PYC_B200_ACT_NONE, a->out, s, st) != 0) return -1;
+    return 0;
+}
+
+}  // extern "C"

@@ -71,3 +71,47 @@ def gemm_inputs(config, M, K, N, dist, bias=True):
         return normal(shape, tensor_seed(config, idx), dist[1])
     a, b = draw((M, K), 0), draw((K, N), 1)
     return (a, b, draw((N,), 2)) if bias else (a, b)
+
+
+# ---- fp8 e4m3 (OCP "fn" variant: no infinities, max finite 448) on the host -------------------------------------
+def _e4m3_table():
+    codes = np.arange(256, dtype=np.uint32)
+    s, e, m = codes >> 7, (codes >> 3) & 0xF, codes & 7
+    val = np.where(e == 0, m.astype(np.float64) * 2.0 ** -9, (8 + m).astype(np.float64) * 2.0 ** (e.astype(np.float64) - 10))
+    val = np.where((e == 15) & (m == 7), np.nan, val)
+    return np.where(s == 1, -val, val).astype(np.float32)
+
+
+E4M3_VALUES = _e4m3_table()          # decode table, index = code
+_E4M3_POS = E4M3_VALUES[:127].astype(np.float64)   # codes 0x00..0x7E ascending, 0 .. 448
+
+
+def e4m3_encode(x):
+    """fp32 -> e4m3 codes, round to nearest even, saturating at +-448."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    ax = np.minimum(np.abs(x).astype(np.float64), 448.0)
+    hi = np.searchsorted(_E4M3_POS, ax, side="left").clip(1, 126)
+    lo = hi - 1
+    dlo, dhi = ax - _E4M3_POS[lo], _E4M3_POS[hi] - ax
+    pick_hi = (dhi < dlo) | ((dhi == dlo) & (hi % 2 == 0))
+    code = np.where(pick_hi, hi, lo).astype(np.uint8)
+    return (code | (np.signbit(x).astype(np.uint8) << 7)).astype(np.uint8)
+
+
+def e4m3_decode(codes):
+    return E4M3_VALUES[np.ascontiguousarray(codes, dtype=np.uint8)]
+
+
+def quantize_weight_per_channel(w):
+    """w [K,N] fp32 -> (e4m3 codes [K,N], scale [N] fp32) with scale = amax over the input dimension / 448."""
+    amax = np.abs(w).max(axis=0)
+    scale = np.where(amax > 0, amax / 448.0, 1.0).astype(np.float32)
+    return e4m3_encode(w / scale[None, :]), scale
+
+
+def ffn_inputs(tokens, hidden, inner, config=5):
+    """Config 5 tensors: x ~ N(0,1) bf16 bits; W1 [H,I], W2 [I,H] ~ N(0,1)/sqrt(fan_in), fp8 codes + per-output-channel scales."""
+    x = to_bf16_bits(normal((tokens, hidden), tensor_seed(config, 0)))
+    w1, s1 = quantize_weight_per_channel(normal((hidden, inner), tensor_seed(config, 1), hidden ** -0.5))
+    w2, s2 = quantize_weight_per_channel(normal((inner, hidden), tensor_seed(config, 2), inner ** -0.5))
+    return x, w1, s1, w2, s2
