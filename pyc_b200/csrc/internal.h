@@ -62,7 +62,7 @@ struct GemmProblem {
     int act = PYC_B200_ACT_NONE;
 };
 
-enum GemmKind { GEMM_TC = 0, GEMM_SIMT = 1 };
+enum GemmKind { GEMM_TC = 0, GEMM_SIMT = 1, GEMM_TC_PAIR = 2 };
 struct GemmConfig {
     const char* symbol;
     GemmKind kind;
@@ -84,6 +84,7 @@ int launch_gemm(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream
 // kernel-file entry points
 int launch_gemm_tc(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream, int* status);
 int launch_gemm_simt(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream);
+int launch_gemm_tc_pair(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream, int* status);
 
 // ---- elementwise / reductions ------------------------------------------------
 int launch_add(pyc_dtype dt, const void* a, const void* b, void* out, size_t n, cudaStream_t s);

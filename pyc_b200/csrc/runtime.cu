@@ -198,6 +198,7 @@ static RegState& reg_state() { static RegState* s = new RegState(); return *s; }
 
 static const GemmConfig kGemmConfigs[] = {
     // symbol suffix           kind       dtypes (bf16|f16 = 8|4, f32 = 2)  bm   bn   bk  st  prio  smem    workload
+    {"tc2_256x256x64_s6", GEMM_TC_PAIR, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 256, 256, 64, 6, 95, 197776, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
     {"tc_128x256x64_s4", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 256, 64, 4, 100, 197744, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
     {"tc_128x128x64_s6", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 128, 64, 6, 90, 197776, PYC_KERNEL_WORKLOAD_SQUARE},
     {"tc_128x64x64_s8", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 64, 64, 8, 80, 197808, PYC_KERNEL_WORKLOAD_SMALL},
@@ -265,8 +266,8 @@ void registry_init_once() {
             // One CTA per SM (persistent) for the tensor-core kernels; SIMT tiles run 2-4 CTAs per SM.
             int prio = c.priority;
             if (c.kind == GEMM_SIMT && d != PYC_DTYPE_F32) prio -= 5;  // any-shape path for 16-bit types
-            reg_add("matmul", gemm_symbol(d, c), prio, c.kind == GEMM_TC ? 0.09 : 0.5, c.kind == GEMM_TC ? 1 : 0, c.smem_bytes,
-                    c.kind == GEMM_TC ? 2 : 1, c.workload);
+            reg_add("matmul", gemm_symbol(d, c), prio, c.kind != GEMM_SIMT ? 0.09 : 0.5, c.kind != GEMM_SIMT ? 1 : 0, c.smem_bytes,
+                    c.kind != GEMM_SIMT ? 2 : 1, c.workload);
         }
     }
     reg_add("conv2d", "b200_conv2d_fprop_bf16", 100, 0.09, 1, 197744, 2, PYC_KERNEL_WORKLOAD_ANY);
@@ -343,6 +344,10 @@ bool gemm_config_supports(const GemmConfig& cfg, const GemmProblem& p) {
     return c && c->cc_major == 10;
 }
 
+// Relative efficiency of the CTA-pair tile in the shape heuristic (the 128x256 single-CTA tile is 1.0).
+// Kept below 1 until a measurement says otherwise: autotune or an explicit symbol can still select the pair kernel.
+static constexpr double kPairEfficiency = 0.9;
+
 const GemmConfig* choose_gemm_config(const GemmProblem& p) {
     {
         std::lock_guard<std::mutex> lk(g_win_mu);
@@ -364,6 +369,7 @@ const GemmConfig* choose_gemm_config(const GemmProblem& p) {
         const double tiles = static_cast<double>((p.M + c.bm - 1) / c.bm) * ((p.N + c.bn - 1) / c.bn);
         double eff, slots;
         if (c.kind == GEMM_TC) { eff = c.bn == 256 ? 1.0 : c.bn == 128 ? 0.85 : 0.6; slots = sms; }
+        else if (c.kind == GEMM_TC_PAIR) { eff = kPairEfficiency; slots = sms / 2; }
         else { eff = (c.bm == 128 ? 1.0 : c.bm == 64 ? 0.8 : 0.55) / 24.0; slots = sms * (c.bm == 128 ? 2.0 : 4.0); }
         const double waves = static_cast<double>(static_cast<long long>((tiles + slots - 1) / slots));
         const double cost = waves * c.bm * c.bn / eff;
@@ -375,10 +381,10 @@ const GemmConfig* choose_gemm_config(const GemmProblem& p) {
 int launch_gemm(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream) {
     if (p.M <= 0 || p.N <= 0 || p.K <= 0 || !p.A || !p.B || !p.D) { set_error("gemm: bad shape or NULL pointer"); return -1; }
     if (!gemm_config_supports(cfg, p)) { set_error("gemm: configuration %s does not support this dtype/shape/alignment", cfg.symbol); return -1; }
-    if (cfg.kind == GEMM_TC) {
+    if (cfg.kind == GEMM_TC || cfg.kind == GEMM_TC_PAIR) {
         int* st = device_status_word();
         if (!st) return -1;
-        return launch_gemm_tc(cfg, p, stream, st);
+        return cfg.kind == GEMM_TC ? launch_gemm_tc(cfg, p, stream, st) : launch_gemm_tc_pair(cfg, p, stream, st);
     }
     return launch_gemm_simt(cfg, p, stream);
 }
