@@ -194,13 +194,11 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
         if (in_mem[v.ext] == MEM_DEVICE) { v.kind = V_INPUT_DIRECT; continue; }
         plan->all_device = false;
         v.kind = V_TEMP;
-        const bool is_static = v.ext < 2 && (static_mask & (1u << v.ext));
-        if (!is_static) {
-            Step s; s.kind = S_H2D; s.out = static_cast<int>(i); s.ext = v.ext; s.bytes = v.bytes;
-            s.via_stage = in_mem[v.ext] == MEM_PAGEABLE;
-            if (s.via_stage) { s.stage_off = plan->stage_bytes; plan->stage_bytes = align_up(plan->stage_bytes + v.bytes, 256); }
-            S.push_back(s);
-        }
+        // static_mask only pins lifetimes (pass 3); whether an upload is dropped is decided by the caller per run.
+        Step s; s.kind = S_H2D; s.out = static_cast<int>(i); s.ext = v.ext; s.bytes = v.bytes;
+        s.via_stage = in_mem[v.ext] == MEM_PAGEABLE;
+        if (s.via_stage) { s.stage_off = plan->stage_bytes; plan->stage_bytes = align_up(plan->stage_bytes + v.bytes, 256); }
+        S.push_back(s);
     }
     std::vector<char> done(n, 0);
     for (size_t i = 0; i < n; ++i) {

@@ -63,13 +63,22 @@ __device__ __forceinline__ float act_fn(float v, int act) {
 // ------------------------------------------------------------------ add ------
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t nvec) {
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        float x[VEC], y[VEC];
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec; i += 2 * stride) {
+        const size_t i2 = i + stride;
+        const bool two = i2 < nvec;
+        float x[VEC], y[VEC], x2[VEC], y2[VEC];
         load_vec<T, VEC>(a + i * VEC, x);
         load_vec<T, VEC>(b + i * VEC, y);
+        if (two) { load_vec<T, VEC>(a + i2 * VEC, x2); load_vec<T, VEC>(b + i2 * VEC, y2); }
 #pragma unroll
         for (int j = 0; j < VEC; ++j) x[j] += y[j];
         store_vec<T, VEC>(out + i * VEC, x);
+        if (two) {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) x2[j] += y2[j];
+            store_vec<T, VEC>(out + i2 * VEC, x2);
+        }
     }
 }
 
@@ -78,19 +87,30 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, const T* __restrict__ add, int add_mode, int act,
                                                       T* __restrict__ out, size_t nvec, size_t cols) {
     const float sadd = add_mode == PYC_B200_ADD_SCALAR ? to_f(add[0]) : 0.0f;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        float v[VEC];
-        load_vec<T, VEC>(x + i * VEC, v);
-        if (add_mode == PYC_B200_ADD_MATRIX || add_mode == PYC_B200_ADD_ROW_BIAS) {
-            float y[VEC];
-            const size_t off = add_mode == PYC_B200_ADD_MATRIX ? i * VEC : (i * VEC) % cols;
-            load_vec<T, VEC>(add + off, y);
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    constexpr int UNROLL = 4;  // independent 16-byte loads in flight per thread
+    for (size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i0 < nvec; i0 += UNROLL * stride) {
+        float v[UNROLL][VEC];
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) v[j] += y[j];
+        for (int u = 0; u < UNROLL; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i < nvec) load_vec<T, VEC>(x + i * VEC, v[u]);
         }
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) v[j] = act_fn(v[j] + sadd, act);
-        store_vec<T, VEC>(out + i * VEC, v);
+        for (int u = 0; u < UNROLL; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i >= nvec) continue;
+            if (add_mode == PYC_B200_ADD_MATRIX || add_mode == PYC_B200_ADD_ROW_BIAS) {
+                float y[VEC];
+                const size_t off = add_mode == PYC_B200_ADD_MATRIX ? i * VEC : (i * VEC) % cols;
+                load_vec<T, VEC>(add + off, y);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) v[u][j] += y[j];
+            }
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[u][j] = act_fn(v[u][j] + sadd, act);
+            store_vec<T, VEC>(out + i * VEC, v[u]);
+        }
     }
 }
 
@@ -111,6 +131,22 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     }
     return v;
+}
+// Two sums in one round.
+template <int THREADS>
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+    if constexpr (THREADS > 32) {
+        const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+        __syncthreads();
+        if (l == 0) { scratch[w] = a; scratch[8 + w] = b; }
+        __syncthreads();
+        a = l < THREADS / 32 ? scratch[l] : 0.0f;
+        b = l < THREADS / 32 ? scratch[8 + l] : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+    }
 }
 template <int THREADS>
 __device__ __forceinline__ float block_max(float v, float* scratch) {
@@ -159,7 +195,7 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
            size_t rows, size_t cols, float eps) {
     constexpr int ROWS_PER_CTA = THREADS >= 128 ? 1 : 128 / THREADS;
     constexpr int NV = CACHED ? VPT : 1;
-    __shared__ float scratch[8];
+    __shared__ float scratch[16];
     const int tid = THREADS >= 128 ? threadIdx.x : (threadIdx.x % THREADS);
     const size_t nvec = cols / VEC;
     for (size_t row = blockIdx.x * static_cast<size_t>(ROWS_PER_CTA) + (THREADS >= 128 ? 0 : threadIdx.x / THREADS);
@@ -195,18 +231,19 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
             s = block_sum<THREADS>(s, scratch);
             if (tid == 0) from_f(out[row], s);
         } else if constexpr (OP == ROW_LAYERNORM) {
-            float s = 0.0f;
+            // One pass: sums of (x - p) and (x - p)^2 with the pivot p = first element of the row, which keeps the
+            // variance free of cancellation whatever the row's mean is.
+            const float pivot = to_f(xr[0]);
+            float s = 0.0f, ss = 0.0f;
             for_each([&](float (&f)[VEC], size_t) {
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) s += f[j];
+                for (int j = 0; j < VEC; ++j) { const float d = f[j] - pivot; s += d; ss = fmaf(d, d, ss); }
             });
-            const float mean = block_sum<THREADS>(s, scratch) / static_cast<float>(cols);
-            float ss = 0.0f;
-            for_each([&](float (&f)[VEC], size_t) {
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) { const float d = f[j] - mean; ss = fmaf(d, d, ss); }
-            });
-            const float rstd = rsqrtf(block_sum<THREADS>(ss, scratch) / static_cast<float>(cols) + eps);
+            block_sum2<THREADS>(s, ss, scratch);
+            const float inv_n = 1.0f / static_cast<float>(cols);
+            const float dmean = s * inv_n;
+            const float mean = pivot + dmean;
+            const float rstd = rsqrtf(fmaxf(ss * inv_n - dmean * dmean, 0.0f) + eps);
             for_each([&](float (&f)[VEC], size_t vi) {
                 float g[VEC], b[VEC];
                 if (gamma) load_vec<T, VEC>(gamma + vi * VEC, g);
@@ -230,12 +267,12 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
             float den = 0.0f;
             for_each([&](float (&f)[VEC], size_t) {
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) den += expf(f[j] - mx);
+                for (int j = 0; j < VEC; ++j) den += __expf(f[j] - mx);
             });
             const float inv = 1.0f / block_sum<THREADS>(den, scratch);
             for_each([&](float (&f)[VEC], size_t vi) {
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) f[j] = expf(f[j] - mx) * inv;
+                for (int j = 0; j < VEC; ++j) f[j] = __expf(f[j] - mx) * inv;
                 store_vec<T, VEC>(orow + vi * VEC, f);
             });
         }

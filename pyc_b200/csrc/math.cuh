@@ -11,7 +11,7 @@ namespace b200 {
 // About a third of the instructions of erff(); the epilogues are otherwise bound by it.
 __device__ __forceinline__ float gelu_erf(float v) {
     const float x = fabsf(v) * 0.70710678118654752f;
-    const float t = __frcp_rn(fmaf(0.3275911f, x, 1.0f));
+    const float t = __fdividef(1.0f, fmaf(0.3275911f, x, 1.0f));  // approximate reciprocal: 1 ulp, inside the formula's own 1.5e-7
     float p = fmaf(1.061405429f, t, -1.453152027f);
     p = fmaf(p, t, 1.421413741f);
     p = fmaf(p, t, -0.284496736f);

@@ -120,12 +120,16 @@ def test_env_switches_on_a_real_device(backend, oracle_lib):
         assert trace.reason.decode().startswith("b200_stream:") and trace.graph_replayed == 0
         os.environ["PYC_CUDA_ENABLE_GRAPH_REPLAY"] = "1"
         os.environ["PYC_CUDA_ASSUME_STATIC_RHS"] = "1"
-        want = oracle_lib.matmul(lhs, rhs)
-        for i in range(3):  # upload, then two runs that skip the RHS upload; LHS changes every run
-            lhs[:] = workloads.normal((64, 64), 100 + i)
-            out[:] = 0
-            backend.dispatch(mod, ins, outs)
-            np.testing.assert_allclose(out, oracle_lib.matmul(lhs, rhs), rtol=0, atol=1e-5 * np.abs(want).max())
+        # fresh buffers and a shape nothing has used yet: the FIRST run must upload the RHS, later runs may skip it
+        lhs2 = workloads.normal((80, 96), 93); rhs2 = workloads.normal((96, 72), 94); out2 = np.zeros((80, 72), np.float32)
+        mod2 = ir.matmul_bias_act(abi.DTYPE_F32, 80, 96, 72, bias=None, act=None)
+        ins2, outs2 = [_host(lhs2, 1), _host(rhs2, 1)], [_host(out2, 1)]
+        scale = np.abs(oracle_lib.matmul(lhs2, rhs2)).max()
+        for i in range(3):  # LHS changes every run, RHS is static
+            lhs2[:] = workloads.normal((80, 96), 100 + i)
+            out2[:] = 0
+            backend.dispatch(mod2, ins2, outs2)
+            np.testing.assert_allclose(out2, oracle_lib.matmul(lhs2, rhs2), rtol=0, atol=1e-5 * scale)
     finally:
         for k in ["PYC_CUDA_FORCE_ERROR", "PYC_CUDA_ENABLE_GRAPH_REPLAY", "PYC_CUDA_ASSUME_STATIC_RHS"]:
             os.environ.pop(k, None)
