@@ -23,6 +23,7 @@
 // (d, seq, batch_heads) so rows past `seq` read as zeros instead of the next head.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "internal.h"
@@ -278,6 +279,236 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Second kernel: the same computation arranged so that TWO CTAs fit on one SM and cover
+// each other's softmax time with their tensor-core work.  Differences from the kernel
+// above: key blocks of 64 (K/V stages of 16 KB, 96 KB of shared memory per CTA), 256
+// TMEM columns per CTA (S0 | S1 | O), each softmax thread reads its 64 scores ONCE, and
+// P never goes through shared memory: it is written back into the TMEM columns its scores
+// came from (packed 2 x 16 bit per column) and the P*V product takes its A operand from
+// TMEM.  S[j&1] cannot be overwritten by Q*K^T of block j+2 before P*V of block j has read
+// it because both are issued, in that order, by the same thread to the in-order MMA pipe.
+// ---------------------------------------------------------------------------------------
+constexpr int BKV2 = 64;
+
+template <int HD>
+struct AttnSmem2 {
+    static constexpr int Q_BYTES = BQ * HD * 2;
+    static constexpr int KV_TILE = BKV2 * HD * 2;      // one [64 x HD] tile
+    static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = Q_BYTES + 2 * KV_TILE, BAR_OFF = Q_BYTES + 4 * KV_TILE;
+    static constexpr int NUM_BARS = 12;
+    static constexpr size_t BYTES = 1024 + BAR_OFF + NUM_BARS * 8 + 16;
+};
+
+template <int HD, int FMT>
+__global__ void __launch_bounds__(192, 2)
+attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, AttnParams ap, int* status) {
+    using SM = AttnSmem2<HD>;
+    using E = AElem<FMT>;
+    using T = typename E::T;
+    constexpr int HALVES = HD / 64;
+    constexpr int Q_SLAB = BQ * 128;                 // [128 rows x 128 B]
+    constexpr int KV_SLAB = BKV2 * 128;              // [64 rows x 128 B]
+    constexpr uint32_t IDESC_QK = make_idesc(FMT, FMT, 0, 0, BQ, BKV2);
+    constexpr uint32_t IDESC_PV = make_idesc(FMT, FMT, 0, 1, BQ, HD);
+    constexpr uint32_t TMEM_COLS = 256;              // S0 @0, S1 @64, O @128
+    constexpr uint32_t O_COL = 128;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + SM::NUM_BARS);
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 24, v_full = bar0 + 40, v_empty = bar0 + 56,
+                   s_full = bar0 + 72, p_full = bar0 + 88, pv_done = bar0 + 96;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_qb = (ap.seq + BQ - 1) / BQ;
+    const int qb = num_qb - 1 - static_cast<int>(blockIdx.x);
+    const int bh = blockIdx.y;
+    const int q0 = qb * BQ;
+    const int kv_blocks_all = (ap.seq + BKV2 - 1) / BKV2;
+    const int nblk = ap.causal ? min(kv_blocks_all, (q0 + BQ + BKV2 - 1) / BKV2) : kv_blocks_all;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full + 8 * i, 1); mbar_init(k_empty + 8 * i, 1);
+            mbar_init(v_full + 8 * i, 1); mbar_init(v_empty + 8 * i, 1);
+            mbar_init(s_full + 8 * i, 1);
+        }
+        mbar_init(p_full, 4);
+        mbar_init(pv_done, 1);
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    const uint32_t sQ = smem_u32(smem + SM::Q_OFF), sK = smem_u32(smem + SM::K_OFF), sV = smem_u32(smem + SM::V_OFF);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, SM::Q_BYTES);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) tma_load_3d(sQ + h * Q_SLAB, &tmQ, q_full, h * 64, q0, bh);
+            for (int j = 0; j < nblk; ++j) {
+                const int st = j & 1;
+                const uint32_t par = ((j >> 1) & 1) ^ 1;
+                if (!mbar_wait(k_empty + 8 * st, par, status, 0x51)) break;
+                mbar_arrive_expect_tx(k_full + 8 * st, SM::KV_TILE);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) tma_load_3d(sK + st * SM::KV_TILE + h * KV_SLAB, &tmK, k_full + 8 * st, h * 64, j * BKV2, bh);
+                if (!mbar_wait(v_empty + 8 * st, par, status, 0x52)) break;
+                mbar_arrive_expect_tx(v_full + 8 * st, SM::KV_TILE);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) tma_load_3d(sV + st * SM::KV_TILE + h * KV_SLAB, &tmV, v_full + 8 * st, h * 64, j * BKV2, bh);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            auto issue_qk = [&](int j) {  // S[j&1] = Q K_j^T, 128 x 64 x HD
+                const int st = j & 1;
+                const uint32_t d = tmem_base + (j & 1) * BKV2;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)
+                    umma_f16(d, make_smem_desc_sw128(sQ + (ks / 4) * Q_SLAB + (ks % 4) * 32, 16, 1024),
+                             make_smem_desc_sw128(sK + st * SM::KV_TILE + (ks / 4) * KV_SLAB + (ks % 4) * 32, 16, 1024), IDESC_QK, ks != 0);
+                umma_commit(s_full + 8 * (j & 1));
+                umma_commit(k_empty + 8 * st);
+            };
+            bool ok = mbar_wait(q_full, 0, status, 0x53);
+            for (int j = 0; j < 2 && j < nblk && ok; ++j) {   // two score blocks in flight before the first P arrives
+                if (!mbar_wait(k_full + 8 * (j & 1), 0, status, 0x54)) { ok = false; break; }
+                tc_fence_after();
+                issue_qk(j);
+            }
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(v_full + 8 * st, (j >> 1) & 1, status, 0x55)) { ok = false; break; }
+                if (!mbar_wait(p_full, j & 1, status, 0x56)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t p_tmem = tmem_base + (j & 1) * BKV2;   // P_j sits where S_j was: 32 columns of packed pairs
+#pragma unroll
+                for (int ks = 0; ks < BKV2 / 16; ++ks)  // O += P_j V_j : 128 x HD x 64, A from TMEM (8 columns per 16 keys)
+                    umma_f16_ts(tmem_base + O_COL, p_tmem + ks * 8, make_smem_desc_sw128(sV + st * SM::KV_TILE + ks * 2048, KV_SLAB, 1024),
+                                IDESC_PV, (j | ks) != 0 ? 1u : 0u);
+                umma_commit(v_empty + 8 * st);
+                umma_commit(pv_done);
+                if (j + 2 < nblk) {   // S[j&1] is free again once P*V of block j is in the pipe ahead of this
+                    const int jn = j + 2;
+                    if (!mbar_wait(k_full + 8 * (jn & 1), (jn >> 1) & 1, status, 0x57)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_qk(jn);
+                }
+            }
+        }
+    } else {
+        const int wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const int qi = q0 + row;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(wq * 32) << 16);
+        float m_run = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        int k_lim = ap.seq;
+        if (ap.causal) k_lim = min(k_lim, qi + 1);
+        for (int j = 0; j < nblk && ok; ++j) {
+            const uint32_t s_addr = lane_addr + (j & 1) * BKV2;
+            if (!mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1, status, 0x58)) { ok = false; break; }
+            tc_fence_after();
+            const int k0 = j * BKV2;
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(s_addr, r0);
+            tmem_ld_32x32(s_addr + 32, r1);
+            tmem_ld_wait();
+            // only blocks that touch the diagonal or the end of the sequence need per-element masking (warp-uniform test)
+            const bool masked = (k0 + BKV2 > ap.seq) || (ap.causal && k0 + BKV2 > q0 + wq * 32 + 1);
+            float m_blk = -INFINITY;
+            if (masked) {
+#pragma unroll
+                for (int t = 0; t < 32; ++t) {
+                    if (k0 + t >= k_lim) r0[t] = 0xff800000u;       // -inf
+                    if (k0 + 32 + t >= k_lim) r1[t] = 0xff800000u;
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < 32; ++t) m_blk = fmaxf(m_blk, fmaxf(__uint_as_float(r0[t]), __uint_as_float(r1[t])));
+            m_blk *= ap.scale_log2;
+            const float m_new = fmaxf(m_run, m_blk);
+            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+            const float alpha = exp2f(m_run - m_use);
+            float l_blk = 0.0f;
+            uint32_t packed[32];
+#pragma unroll
+            for (int t = 0; t < 32; t += 2) {
+                const float a0 = exp2f(fmaf(__uint_as_float(r0[t]), ap.scale_log2, -m_use)), a1 = exp2f(fmaf(__uint_as_float(r0[t + 1]), ap.scale_log2, -m_use));
+                const float b0 = exp2f(fmaf(__uint_as_float(r1[t]), ap.scale_log2, -m_use)), b1 = exp2f(fmaf(__uint_as_float(r1[t + 1]), ap.scale_log2, -m_use));
+                l_blk += (a0 + a1) + (b0 + b1);
+                packed[t / 2] = E::pack(a0, a1);          // keys k0 + t, t+1      -> column t/2
+                packed[16 + t / 2] = E::pack(b0, b1);     // keys k0 + 32 + t, ..  -> column 16 + t/2
+            }
+            l_run = l_run * alpha + l_blk;
+            m_run = m_new;
+            // O is shared with the previous block's P*V: it must have finished before O is rescaled or P_j replaces S_j... (S_j itself
+            // was read above; P_{j-1} lives in the other buffer).
+            if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, status, 0x59)) { ok = false; break; }
+            tc_fence_after();
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(lane_addr + O_COL + c * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int t = 0; t < 32; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * alpha);
+                    tmem_st_32x32(lane_addr + O_COL + c * 32, o);
+                }
+            }
+            tmem_st_32x32(s_addr, packed);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        if (ok && mbar_wait(pv_done, (nblk - 1) & 1, status, 0x5a)) {
+            tc_fence_after();
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            T* orow = reinterpret_cast<T*>(ap.out) + (static_cast<size_t>(bh) * ap.seq + qi) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(lane_addr + O_COL + c * 32, r);
+                tmem_ld_wait();
+                if (qi < ap.seq) {
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 u;
+                        u.x = E::pack(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv);
+                        u.y = E::pack(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv);
+                        u.z = E::pack(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv);
+                        u.w = E::pack(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv);
+                        dst[q4] = u;
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*reinterpret_cast<volatile int*>(status) != ST_OK) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
 // Any-shape path (fp32, head sizes other than 64/128, unaligned pointers): one warp per
 // query row, online softmax over the keys, lanes split the head dimension.
 __device__ __forceinline__ float ald(const float* p) { return __ldg(p); }
@@ -337,26 +568,43 @@ int launch_rowwarp(const void* q, const void* k, const void* v, void* o, int bh,
 template <int HD, int FMT>
 int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void* k, const void* v, void* out, float scale, int causal,
                         cudaStream_t stream, int* status) {
-    auto kernel = attention_tc_kernel<HD, FMT>;
-    // At least 120 KB so that two CTAs never share an SM: each one takes all 512 TMEM columns.
-    constexpr size_t smem = AttnSmem<HD>::BYTES > 120 * 1024 ? AttnSmem<HD>::BYTES : 120 * 1024;
-    static bool attr_set[16] = {};
+    // PYC_B200_ATTENTION_KERNEL=1 selects the first kernel (128-key blocks, P through shared memory, one CTA per SM);
+    // the default is the second one (64-key blocks, P in TMEM, two CTAs per SM).
+    const char* pick = getenv("PYC_B200_ATTENTION_KERNEL");
+    const bool first = pick && pick[0] == '1';
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 16 && !attr_set[dev]) {
-        B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        attr_set[dev] = true;
-    }
     CUtensorMap tq, tk, tv;
     const uint64_t dims[3] = {static_cast<uint64_t>(HD), static_cast<uint64_t>(seq), static_cast<uint64_t>(bh)};
     const uint64_t str[2] = {static_cast<uint64_t>(HD) * 2, static_cast<uint64_t>(seq) * HD * 2};
-    const uint32_t box[3] = {64, 128, 1};
-    if (encode_tmap(&tq, q, 2, 3, dims, str, box, true) != 0 || encode_tmap(&tk, k, 2, 3, dims, str, box, true) != 0 ||
-        encode_tmap(&tv, v, 2, 3, dims, str, box, true) != 0) return -1;
+    const uint32_t box_q[3] = {64, 128, 1};
+    const uint32_t box_kv[3] = {64, static_cast<uint32_t>(first ? BKV : BKV2), 1};
+    if (encode_tmap(&tq, q, 2, 3, dims, str, box_q, true) != 0 || encode_tmap(&tk, k, 2, 3, dims, str, box_kv, true) != 0 ||
+        encode_tmap(&tv, v, 2, 3, dims, str, box_kv, true) != 0) return -1;
     AttnParams ap;
     ap.seq = seq; ap.batch_heads = bh; ap.causal = causal ? 1 : 0; ap.scale_log2 = scale * 1.4426950408889634f; ap.out = out;
     dim3 grid((seq + BQ - 1) / BQ, bh);
-    kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
+    if (first) {
+        auto kernel = attention_tc_kernel<HD, FMT>;
+        // At least 120 KB so that two CTAs never share an SM: each one takes all 512 TMEM columns.
+        constexpr size_t smem = AttnSmem<HD>::BYTES > 120 * 1024 ? AttnSmem<HD>::BYTES : 120 * 1024;
+        static bool attr_set[16] = {};
+        if (dev < 16 && !attr_set[dev]) {
+            B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            attr_set[dev] = true;
+        }
+        kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
+    } else {
+        auto kernel = attention_tc2_kernel<HD, FMT>;
+        // Never less than 76 KB: at most two CTAs per SM, because each takes 256 of the 512 TMEM columns.
+        constexpr size_t smem = AttnSmem2<HD>::BYTES > 76 * 1024 ? AttnSmem2<HD>::BYTES : 76 * 1024;
+        static bool attr_set2[16] = {};
+        if (dev < 16 && !attr_set2[dev]) {
+            B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            attr_set2[dev] = true;
+        }
+        kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
+    }
     B200_CUDA_OK(cudaGetLastError());
     count_launch();
     return 0;

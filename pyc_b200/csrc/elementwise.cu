@@ -114,6 +114,35 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, 
     }
 }
 
+// Row bias (+ activation): every thread owns one 16-byte column slot, keeps its slice of the bias in registers and
+// walks down the rows, so there is no index arithmetic beyond one add per row.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) row_bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, int act, T* __restrict__ out,
+                                                          size_t rows, size_t cols) {
+    const size_t vec_per_row = cols / VEC;
+    const size_t col_vec = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (col_vec >= vec_per_row) return;
+    float b[VEC];
+    load_vec<T, VEC>(bias + col_vec * VEC, b);
+    constexpr int UNROLL = 4;
+    for (size_t r0 = blockIdx.y; r0 < rows; r0 += static_cast<size_t>(gridDim.y) * UNROLL) {
+        float v[UNROLL][VEC];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const size_t r = r0 + static_cast<size_t>(u) * gridDim.y;
+            if (r < rows) load_vec<T, VEC>(x + r * cols + col_vec * VEC, v[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const size_t r = r0 + static_cast<size_t>(u) * gridDim.y;
+            if (r >= rows) continue;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[u][j] = act_fn(v[u][j] + b[j], act);
+            store_vec<T, VEC>(out + r * cols + col_vec * VEC, v[u]);
+        }
+    }
+}
+
 // ------------------------------------------------------------ row reductions --
 enum RowOp { ROW_LAYERNORM = 0, ROW_SOFTMAX = 1, ROW_SUM = 2 };
 
@@ -347,7 +376,16 @@ int launch_bias_act_typed(const void* x, const void* add, int add_mode, int act,
     constexpr int V = VecInfo<T>::N;
     const size_t n = rows * cols;
     if (!add) add_mode = PYC_B200_ADD_NONE;
-    if (cols % V == 0 && aligned16(x) && aligned16(out) && (add_mode == PYC_B200_ADD_SCALAR || aligned16(add))) {
+    if (add_mode == PYC_B200_ADD_ROW_BIAS && cols % V == 0 && aligned16(x) && aligned16(out) && aligned16(add)) {
+        const size_t vec_per_row = cols / V;
+        const unsigned threads = vec_per_row >= 256 ? 256 : static_cast<unsigned>((vec_per_row + 31) / 32 * 32);
+        const unsigned gx = static_cast<unsigned>((vec_per_row + threads - 1) / threads);
+        size_t gy = (static_cast<size_t>(sm_count()) * 8 * 256 / threads + gx - 1) / gx;  // fill every SM's thread slots
+        if (gy > rows) gy = rows;
+        if (gy > 65535) gy = 65535;
+        row_bias_act_kernel<T, V><<<dim3(gx, static_cast<unsigned>(gy)), threads, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add), act,
+                                                                                      static_cast<T*>(out), rows, cols);
+    } else if (cols % V == 0 && aligned16(x) && aligned16(out) && (add_mode == PYC_B200_ADD_SCALAR || aligned16(add))) {
         bias_act_kernel<T, V><<<flat_grid(n / V, 256), 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add), add_mode, act, static_cast<T*>(out), n / V, cols);
     } else {
         bias_act_kernel<T, 1><<<flat_grid(n, 256), 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add), add_mode, act, static_cast<T*>(out), n, cols);
