@@ -23,6 +23,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "internal.h"
@@ -43,6 +45,8 @@ struct Epilogue {
     const void* add;
     float alpha, add_scale;
     int add_mode, act, vec_ok;
+    int group_m;     // M-tiles per rasterisation group
+    int l2_hints;    // 0 none, 1 A evict_last + B evict_first, 2 both evict_last
 };
 
 __device__ __forceinline__ float apply_act(float v, int act) {
@@ -78,11 +82,11 @@ template <> struct Elem<0> {
     }
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-    const int group = GROUP_M * tiles_n;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+    const int group = group_m * tiles_n;
     const int g = tile / group;
-    const int first = g * GROUP_M;
-    const int gm = min(GROUP_M, tiles_m - first);
+    const int first = g * group_m;
+    const int gm = min(group_m, tiles_m - first);
     const int local = tile - g * group;
     tm = first + local % gm;
     tn = local / gm;
@@ -139,21 +143,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            const uint64_t pol_a = l2_policy_evict_last();
+            const uint64_t pol_b = ep.l2_hints == 2 ? l2_policy_evict_last() : l2_policy_evict_first();
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 int tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                tile_coords(tile, tiles_m, tiles_n, ep.group_m, tm, tn);
                 const int m0 = tm * BM, n0 = tn * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, status, 1)) { ok = false; break; }
                     const uint32_t fb = full0 + 8 * stage;
                     mbar_arrive_expect_tx(fb, STAGE_TX);
-                    tma_load_2d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, fb, kb * BK, m0);
-                    const uint32_t bdst = smem_u32(sB + stage * B_STAGE_BYTES);
-                    if (B_KMAJOR) {
-                        tma_load_2d(bdst, &tmB, fb, kb * BK, n0);
-                    } else {
+                    const uint32_t adst = smem_u32(sA + stage * A_STAGE_BYTES), bdst = smem_u32(sB + stage * B_STAGE_BYTES);
+                    if (ep.l2_hints) {
+                        tma_load_2d_hint(adst, &tmA, fb, kb * BK, m0, pol_a);
+                        if (B_KMAJOR) {
+                            tma_load_2d_hint(bdst, &tmB, fb, kb * BK, n0, pol_b);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(bdst + j * (BK * 128), &tmB, fb, n0 + j * 64, kb * BK);
+                            for (int j = 0; j < BN / 64; ++j) tma_load_2d_hint(bdst + j * (BK * 128), &tmB, fb, n0 + j * 64, kb * BK, pol_b);
+                        }
+                    } else {
+                        tma_load_2d(adst, &tmA, fb, kb * BK, m0);
+                        if (B_KMAJOR) {
+                            tma_load_2d(bdst, &tmB, fb, kb * BK, n0);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j) tma_load_2d(bdst + j * (BK * 128), &tmB, fb, n0 + j * 64, kb * BK);
+                        }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -193,7 +209,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
             int tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            tile_coords(tile, tiles_m, tiles_n, ep.group_m, tm, tn);
             const int row = tm * BM + wq * 32 + lane;
             const int n0 = tn * BN;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase, status, 4)) break;
@@ -270,6 +286,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
 }
 
+// Tile rasterisation knobs: PYC_B200_GEMM_GROUP_M (M-tiles per group) and PYC_B200_GEMM_L2_HINTS (0, 1, 2) override the defaults.
+inline void tile_order_from_env(int* group_m, int* l2_hints) {
+    *group_m = GROUP_M;
+    *l2_hints = 0;
+    if (const char* g = getenv("PYC_B200_GEMM_GROUP_M")) { const int v = atoi(g); if (v >= 1 && v <= 1024) *group_m = v; }
+    if (const char* h = getenv("PYC_B200_GEMM_L2_HINTS")) { const int v = atoi(h); if (v >= 0 && v <= 2) *l2_hints = v; }
+}
+
 template <int BN, int STAGES>
 constexpr size_t tc_smem_bytes() {
     return 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16;
@@ -300,6 +324,7 @@ int launch_instance(const GemmProblem& p, cudaStream_t stream, int* status) {
                          (ep.add_mode == PYC_B200_ADD_NONE || ep.add_mode == PYC_B200_ADD_SCALAR ||
                           reinterpret_cast<uintptr_t>(p.add) % 16 == 0);
     ep.vec_ok = aligned ? 1 : 0;
+    tile_order_from_env(&ep.group_m, &ep.l2_hints);
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
     kernel<<<grid, 192, smem, stream>>>(tmA, tmB, ep, p.M, p.N, p.K, status);
@@ -382,6 +407,7 @@ int launch_static_instance(const GemmProblem& p, cudaStream_t stream, StaticDevi
     ep.add_mode = p.add ? p.add_mode : PYC_B200_ADD_NONE; ep.act = p.act;
     ep.vec_ok = ((reinterpret_cast<uintptr_t>(p.D) % 16 == 0) && (p.N % 8 == 0) &&
                  (ep.add_mode == PYC_B200_ADD_NONE || ep.add_mode == PYC_B200_ADD_SCALAR || reinterpret_cast<uintptr_t>(p.add) % 16 == 0)) ? 1 : 0;
+    tile_order_from_env(&ep.group_m, &ep.l2_hints);
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     // The block keeps whatever the previous call left: the status word must start at zero.
     B200_CUDA_OK(cudaMemsetAsync(sd.scratch, 0, kStaticScratchBytes, stream));

@@ -27,7 +27,7 @@ def _dev(dtype, shape, seed, std):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "add", "bias_gelu", "layernorm", "softmax", "reduce_sum", "attention", "conv2d"])
+    ap.add_argument("op", choices=["gemm", "add", "bias_gelu", "layernorm", "softmax", "reduce_sum", "attention", "conv2d", "ffn", "gemm_fp8"])
     ap.add_argument("--dtype", default="bf16", choices=list(DT))
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=16384); ap.add_argument("--cols", type=int, default=8192)
@@ -35,11 +35,17 @@ def main():
     ap.add_argument("--causal", type=int, default=1)
     ap.add_argument("--conv", default="64,56,56,64,64", help="N,H,W,C,K (3x3, pad 1, stride 1)")
     ap.add_argument("--epilogue", default="bias_gelu", choices=["none", "bias_relu", "bias_gelu"])
+    ap.add_argument("--tokens", type=int, default=8192); ap.add_argument("--hidden", type=int, default=4096); ap.add_argument("--inner", type=int, default=16384)
     ap.add_argument("--symbol", default=None)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=1)
     a = ap.parse_args()
     dt = DT[a.dtype]
+    import os
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
     backend.load()
     es = abi.DTYPE_SIZE[dt]
     if a.op == "gemm":
@@ -59,6 +65,20 @@ def main():
                "reduce_sum": lambda: backend.reduce_sum(dt, X.data_ptr(), O.data_ptr(), a.rows, a.cols)}[a.op]
         nbytes = {"add": 3, "reduce_sum": 1}.get(a.op, 2) * n * es
         work = ("GB/s", nbytes / 1e9)
+    elif a.op == "gemm_fp8":
+        A = torch.randint(0, 120, (a.m, a.k), dtype=torch.uint8, device="cuda"); B = torch.randint(0, 120, (a.k, a.n), dtype=torch.uint8, device="cuda")
+        rs = torch.ones(a.m, device="cuda"); cs = torch.ones(a.n, device="cuda"); D = torch.zeros((a.m, a.n), dtype=torch.int16, device="cuda")
+        run = lambda: backend.gemm_fp8(a.m, a.n, a.k, A.data_ptr(), B.data_ptr(), D.data_ptr(), rs.data_ptr(), cs.data_ptr(), None, abi.ACT_GELU)
+        work = ("TFLOP/s", 2.0 * a.m * a.n * a.k / 1e12)
+    elif a.op == "ffn":
+        # benchmark configuration 5; with WORLD_SIZE > 1 (torchrun) the inner dimension is sharded and one all-reduce ends the block
+        from . import ffn
+        xb, w1, s1, w2, s2 = workloads.ffn_inputs(a.tokens, a.hidden, a.inner)
+        w1r, s1r, w2r = ffn.shard_weights(w1, s1, w2, rank, world)
+        blk = ffn.FfnBlock(a.tokens, a.hidden, a.inner // world, w1r, s1r, w2r, s2, torch)
+        X = torch.from_numpy(xb.view(np.int16)).cuda()
+        run = lambda: blk.run(X)
+        work = ("TFLOP/s (whole block, all ranks)", 4.0 * a.tokens * a.hidden * a.inner / 1e12)
     elif a.op == "attention":
         shape = (a.batch_heads, a.seq, a.d)
         Q, K_, V = _dev(dt, shape, 7, 1.0), _dev(dt, shape, 8, 1.0), _dev(dt, shape, 9, 1.0); O = torch.zeros_like(Q)
@@ -82,7 +102,15 @@ def main():
     torch.cuda.synchronize()
     assert backend.device_status() == 0
     ms = e0.elapsed_time(e1) / a.iters
-    print(f"{a.op} {a.dtype}: {ms:.4f} ms/launch, {work[1] / (ms * 1e-3):.1f} {work[0]}")
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t[0])
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+        if rank != 0:
+            return
+    print(f"{a.op} {a.dtype} x{world}: {ms:.4f} ms/launch, {work[1] / (ms * 1e-3):.1f} {work[0]}")
 
 
 if __name__ == "__main__":
