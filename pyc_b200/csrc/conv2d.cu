@@ -168,10 +168,23 @@ conv2d_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
                 if (col0 < cp.K && row_ok) {         // lanes outside the image only skip the stores; every lane stays in the loop
                     float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float x = __uint_as_float(rr[j]);
-                        if (bias && col0 + j < cp.K) x += E::to_f(bias[col0 + j]);
-                        v[j] = cp.relu ? fmaxf(x, 0.0f) : x;
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]);
+                    if (bias) {
+                        if (vec_ok && col0 + 32 <= cp.K && reinterpret_cast<uintptr_t>(bias) % 16 == 0) {
+#pragma unroll
+                            for (int qd = 0; qd < 4; ++qd) {  // 16-byte loads, the same address in every lane
+                                union { uint4 u; T t[8]; } b;
+                                b.u = __ldg(reinterpret_cast<const uint4*>(bias + col0) + qd);
+#pragma unroll
+                                for (int t = 0; t < 8; ++t) v[qd * 8 + t] += E::to_f(b.t[t]);
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j) if (col0 + j < cp.K) v[j] += E::to_f(bias[col0 + j]);
+                        }
+                    }
+                    if (cp.relu) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
                     }
                     if (vec_ok && col0 + 32 <= cp.K) {
                         uint4* dst = reinterpret_cast<uint4*>(orow + col0);

@@ -133,7 +133,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     } else {
         const int wq = warp & 3;
         int it = 0;
-        const bool vec_ok = (N % 8 == 0) && (reinterpret_cast<uintptr_t>(ep.D) % 16 == 0);
+        const bool vec_ok = (N % 8 == 0) && (reinterpret_cast<uintptr_t>(ep.D) % 16 == 0) &&
+                            (reinterpret_cast<uintptr_t>(ep.col_scale) % 16 == 0) && (reinterpret_cast<uintptr_t>(ep.bias) % 16 == 0);
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
             int tm, tn;
@@ -152,17 +153,41 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int col0 = n0 + c * 32;  // warp-uniform
                 if (col0 < N && row < M) {
                     float v[32];
+                    const bool full_chunk = vec_ok && col0 + 32 <= N;
+                    if (full_chunk) {  // scales and bias as 16-byte loads: every lane reads the same 128 / 64 bytes (broadcast)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int col = col0 + j;
-                        float x = __uint_as_float(r[j]) * rs;
-                        if (col < N) {
-                            if (ep.col_scale) x *= __ldg(ep.col_scale + col);
-                            if (ep.bias) x += __bfloat162float(ep.bias[col]);
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * rs;
+                        if (ep.col_scale) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const float4 c4 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + col0) + q);
+                                v[q * 4 + 0] *= c4.x; v[q * 4 + 1] *= c4.y; v[q * 4 + 2] *= c4.z; v[q * 4 + 3] *= c4.w;
+                            }
                         }
-                        v[j] = apply_activation(x, ep.act);
+                        if (ep.bias) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const uint4 u = __ldg(reinterpret_cast<const uint4*>(ep.bias + col0) + q);
+                                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                                for (int t = 0; t < 4; ++t) { v[q * 8 + 2 * t] += __uint_as_float(w[t] << 16); v[q * 8 + 2 * t + 1] += __uint_as_float(w[t] & 0xffff0000u); }
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = apply_activation(v[j], ep.act);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int col = col0 + j;
+                            float x = __uint_as_float(r[j]) * rs;
+                            if (col < N) {
+                                if (ep.col_scale) x *= __ldg(ep.col_scale + col);
+                                if (ep.bias) x += __bfloat162float(ep.bias[col]);
+                            }
+                            v[j] = apply_activation(x, ep.act);
+                        }
                     }
-                    if (vec_ok && col0 + 32 <= N) {
+                    if (full_chunk) {
                         uint4* dst = reinterpret_cast<uint4*>(drow + col0);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
