@@ -28,9 +28,12 @@ def shard_weights(w1, s1, w2, rank, world, b1=None):
 
 
 class FfnBlock:
-    """Device-resident shard of one FFN block plus its workspace; call run() once per step."""
+    """Device-resident shard of one FFN block plus its workspace; call run() once per step.
 
-    def __init__(self, tokens, hidden, inner_local, w1, s1, w2, s2, torch, group=None):
+    With more than one rank the tokens are processed in `chunks` row slices: the all-reduce of slice i runs on a second
+    stream while slice i+1 is still in its GEMMs, so only the last slice's collective is exposed."""
+
+    def __init__(self, tokens, hidden, inner_local, w1, s1, w2, s2, torch, group=None, chunks=None):
         self.torch, self.group = torch, group
         self.tokens, self.hidden, self.inner = tokens, hidden, inner_local
         dev = "cuda"
@@ -38,16 +41,41 @@ class FfnBlock:
         self.s1 = torch.from_numpy(np.ascontiguousarray(s1, dtype=np.float32)).to(dev)
         self.w2 = torch.from_numpy(np.ascontiguousarray(w2)).to(dev)
         self.s2 = torch.from_numpy(np.ascontiguousarray(s2, dtype=np.float32)).to(dev)
-        self.ws_bytes = backend.ffn_workspace_bytes(tokens, hidden, inner_local)
+        dist = torch.distributed
+        self.parallel = group is not None or (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1)
+        if chunks is None:
+            chunks = 4 if self.parallel and tokens % 4 == 0 and tokens // 4 >= 1024 else 1
+        if tokens % chunks:
+            raise ValueError(f"{tokens} tokens do not split into {chunks} equal chunks")
+        self.chunks, self.rows = chunks, tokens // chunks
+        self.ws_bytes = backend.ffn_workspace_bytes(self.rows, hidden, inner_local)
+        # one workspace per chunk in flight: chunk i+1 may start while chunk i's output is still being reduced,
+        # but its scratch is free as soon as its last GEMM has been issued on the same stream
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
         self.out = torch.zeros((tokens, hidden), dtype=torch.bfloat16, device=dev)
+        self.comm_stream = torch.cuda.Stream() if self.parallel and chunks > 1 else None
 
     def run(self, x_dev, stream=None):
         """x_dev: [T,H] bf16 (or int16 bit pattern) device tensor.  Returns the (all-reduced) bf16 output tensor."""
         torch = self.torch
-        s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
-        backend.ffn_block(self.tokens, self.hidden, self.inner, x_dev.data_ptr(), self.w1.data_ptr(), self.s1.data_ptr(),
-                          self.w2.data_ptr(), self.s2.data_ptr(), self.out.data_ptr(), self.ws.data_ptr(), self.ws_bytes, stream=s)
-        if self.group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1):
-            torch.distributed.all_reduce(self.out, group=self.group)
+        cur = torch.cuda.current_stream()
+        s = stream if stream is not None else cur.cuda_stream
+        row_bytes = self.hidden * 2
+        for c in range(self.chunks):
+            off = c * self.rows
+            backend.ffn_block(self.rows, self.hidden, self.inner, x_dev.data_ptr() + off * row_bytes, self.w1.data_ptr(), self.s1.data_ptr(),
+                              self.w2.data_ptr(), self.s2.data_ptr(), self.out.data_ptr() + off * row_bytes, self.ws.data_ptr(), self.ws_bytes, stream=s)
+            if not self.parallel:
+                continue
+            part = self.out[off:off + self.rows]
+            if self.comm_stream is None:
+                torch.distributed.all_reduce(part, group=self.group)
+            else:
+                ev = torch.cuda.Event()
+                ev.record(cur)
+                self.comm_stream.wait_event(ev)
+                with torch.cuda.stream(self.comm_stream):
+                    torch.distributed.all_reduce(part, group=self.group)
+        if self.comm_stream is not None:
+            cur.wait_stream(self.comm_stream)
         return self.out

@@ -36,6 +36,7 @@ def main():
     ap.add_argument("--conv", default="64,56,56,64,64", help="N,H,W,C,K (3x3, pad 1, stride 1)")
     ap.add_argument("--epilogue", default="bias_gelu", choices=["none", "bias_relu", "bias_gelu"])
     ap.add_argument("--tokens", type=int, default=8192); ap.add_argument("--hidden", type=int, default=4096); ap.add_argument("--inner", type=int, default=16384)
+    ap.add_argument("--chunks", type=int, default=None, help="ffn: row slices whose all-reduce overlaps the next slice (default: 4 when tensor parallel)")
     ap.add_argument("--symbol", default=None)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=1)
@@ -75,7 +76,7 @@ def main():
         from . import ffn
         xb, w1, s1, w2, s2 = workloads.ffn_inputs(a.tokens, a.hidden, a.inner)
         w1r, s1r, w2r = ffn.shard_weights(w1, s1, w2, rank, world)
-        blk = ffn.FfnBlock(a.tokens, a.hidden, a.inner // world, w1r, s1r, w2r, s2, torch)
+        blk = ffn.FfnBlock(a.tokens, a.hidden, a.inner // world, w1r, s1r, w2r, s2, torch, chunks=a.chunks)
         X = torch.from_numpy(xb.view(np.int16)).cuda()
         run = lambda: blk.run(X)
         work = ("TFLOP/s (whole block, all ranks)", 4.0 * a.tokens * a.hidden * a.inner / 1e12)
