@@ -12,6 +12,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "internal.h"
 #include "math.cuh"
 
@@ -134,6 +136,102 @@ gemm_simt_kernel(SimtParams p) {
     }
 }
 
+// Latency variant for small fp32 problems (the 512^3 graph): 32 x 64 tile, 128 threads, 4 x 4 outputs per thread,
+// operands brought in with 16-byte cp.async into a 3-stage ring of 32-deep k-slices, 16-byte shared-memory reads
+// (8 loads per 64 FMAs).  One wave of small CTAs covers most of the SMs; the ring hides the L2 latency that the
+// register-prefetch kernel above exposes when only one CTA sits on an SM.  Needs K % 4 == 0, N % 4 == 0, 16-byte
+// aligned A and B, row-major B.
+constexpr int LBM = 32, LBN = 64, LBK = 32, LSTAGES = 3, LPAD = 4;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__global__ void __launch_bounds__(128)
+gemm_simt_latency_kernel(SimtParams p) {
+    __shared__ __align__(16) float As[LSTAGES][LBM][LBK + LPAD];
+    __shared__ __align__(16) float Bs[LSTAGES][LBK][LBN];
+    const float* A = reinterpret_cast<const float*>(p.A);
+    const float* B = reinterpret_cast<const float*>(p.B);
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * LBM, n0 = blockIdx.x * LBN;
+    const int M = p.M, N = p.N, K = p.K;
+    const int steps = (K + LBK - 1) / LBK;
+
+    auto issue = [&](int step, int buf) {
+        const int k0 = step * LBK;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {   // A: 32 rows x 8 chunks of 4 floats
+            const int c = tid + i * 128, r = c >> 3, kc = (c & 7) * 4;
+            const bool ok = (m0 + r) < M && (k0 + kc) < K;
+            cp_async16(&As[buf][r][kc], ok ? A + static_cast<size_t>(m0 + r) * K + k0 + kc : A, ok);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {   // B: 32 k-rows x 16 chunks of 4 floats
+            const int c = tid + i * 128, r = c >> 4, nc = (c & 15) * 4;
+            const bool ok = (k0 + r) < K && (n0 + nc) < N;
+            cp_async16(&Bs[buf][r][nc], ok ? B + static_cast<size_t>(k0 + r) * N + n0 + nc : B, ok);
+        }
+    };
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+#pragma unroll
+    for (int s = 0; s < LSTAGES - 1; ++s) { if (s < steps) issue(s, s); cp_async_commit(); }
+    for (int step = 0; step < steps; ++step) {
+        cp_async_wait<LSTAGES - 2>();
+        __syncthreads();                       // slice `step` has landed for everyone; the slot refilled below was read last step
+        const int nxt = step + LSTAGES - 1;
+        if (nxt < steps) issue(nxt, nxt % LSTAGES);
+        cp_async_commit();
+        const int buf = step % LSTAGES;
+#pragma unroll
+        for (int k4 = 0; k4 < LBK / 4; ++k4) {
+            float4 a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(&As[buf][ty * 4 + i][k4 * 4]);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) b[kk] = *reinterpret_cast<const float4*>(&Bs[buf][k4 * 4 + kk][tx * 4]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {   // ascending k inside the slice, as everywhere else
+                const float av[4] = {a[i].x, a[i].y, a[i].z, a[i].w};
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    acc[i][0] = fmaf(av[kk], b[kk].x, acc[i][0]); acc[i][1] = fmaf(av[kk], b[kk].y, acc[i][1]);
+                    acc[i][2] = fmaf(av[kk], b[kk].z, acc[i][2]); acc[i][3] = fmaf(av[kk], b[kk].w, acc[i][3]);
+                }
+            }
+        }
+    }
+
+    float* D = reinterpret_cast<float*>(p.D);
+    const float* add = reinterpret_cast<const float*>(p.add);
+    const float sadd = p.add_mode == PYC_B200_ADD_SCALAR ? p.add_scale * __ldg(add) : 0.0f;
+    const int c0 = n0 + tx * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = m0 + ty * 4 + i;
+        if (r >= M || c0 >= N) continue;   // N % 4 == 0: a thread's four columns are in or out together
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[j] = p.alpha * acc[i][j] + sadd;
+            if (p.add_mode == PYC_B200_ADD_ROW_BIAS) v[j] += p.add_scale * __ldg(add + c0 + j);
+            else if (p.add_mode == PYC_B200_ADD_MATRIX) v[j] += p.add_scale * __ldg(add + static_cast<size_t>(r) * N + c0 + j);
+            v[j] = act_fn(v[j], p.act);
+        }
+        *reinterpret_cast<float4*>(D + static_cast<size_t>(r) * N + c0) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+}
+
 template <typename T, int BM, int BN, int TM, int TN>
 int launch_one(const SimtParams& sp, cudaStream_t stream) {
     dim3 grid((sp.N + BN - 1) / BN, (sp.M + BM - 1) / BM);
@@ -143,8 +241,23 @@ int launch_one(const SimtParams& sp, cudaStream_t stream) {
     return 0;
 }
 
+bool latency_kernel_ok(const SimtParams& sp) {
+    return !sp.b_col_major && sp.K % 4 == 0 && sp.N % 4 == 0 && reinterpret_cast<uintptr_t>(sp.A) % 16 == 0 &&
+           reinterpret_cast<uintptr_t>(sp.B) % 16 == 0 && reinterpret_cast<uintptr_t>(sp.D) % 16 == 0;
+}
+
 template <typename T>
 int launch_typed(const GemmConfig& cfg, const SimtParams& sp, cudaStream_t stream) {
+    if constexpr (std::is_same<T, float>::value) {
+        if (cfg.bm == 32 && cfg.bn == 64 && cfg.bk == 32) {
+            if (!latency_kernel_ok(sp)) { set_error("simt_async_32x64x32 needs row-major B, K %% 4 == 0, N %% 4 == 0 and 16-byte aligned pointers"); return -1; }
+            dim3 grid((sp.N + LBN - 1) / LBN, (sp.M + LBM - 1) / LBM);
+            gemm_simt_latency_kernel<<<grid, 128, 0, stream>>>(sp);
+            B200_CUDA_OK(cudaGetLastError());
+            count_launch();
+            return 0;
+        }
+    }
     if (cfg.bm == 128 && cfg.bn == 128) return launch_one<T, 128, 128, 8, 8>(sp, stream);
     if (cfg.bm == 64 && cfg.bn == 64) return launch_one<T, 64, 64, 4, 4>(sp, stream);
     if (cfg.bm == 32 && cfg.bn == 64) return launch_one<T, 32, 64, 2, 4>(sp, stream);

@@ -204,6 +204,7 @@ static const GemmConfig kGemmConfigs[] = {
     {"tc_128x64x64_s8", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 64, 64, 8, 80, 197808, PYC_KERNEL_WORKLOAD_SMALL},
     {"simt_128x128x16", GEMM_SIMT, (1 << PYC_DTYPE_F32) | (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 128, 16, 2, 30, 33792, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
     {"simt_64x64x16", GEMM_SIMT, (1 << PYC_DTYPE_F32) | (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 64, 64, 16, 2, 20, 17408, PYC_KERNEL_WORKLOAD_SQUARE},
+    {"simt_async_32x64x32", GEMM_SIMT, (1 << PYC_DTYPE_F32), 32, 64, 32, 3, 25, 38400, PYC_KERNEL_WORKLOAD_SMALL},
     {"simt_32x64x16", GEMM_SIMT, (1 << PYC_DTYPE_F32) | (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 32, 64, 16, 2, 10, 13312, PYC_KERNEL_WORKLOAD_SMALL},
 };
 const GemmConfig* gemm_configs(int* count) {
@@ -335,7 +336,12 @@ void remember_gemm_winner(pyc_dtype dtype, int M, int N, int K, const GemmConfig
 
 bool gemm_config_supports(const GemmConfig& cfg, const GemmProblem& p) {
     if (!(cfg.dtype_mask & (1 << p.dtype))) return false;
-    if (cfg.kind == GEMM_SIMT) return true;
+    if (cfg.kind == GEMM_SIMT) {
+        if (cfg.bk == 32)  // the cp.async latency tile
+            return !p.b_col_major && p.K % 4 == 0 && p.N % 4 == 0 && reinterpret_cast<uintptr_t>(p.A) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(p.B) % 16 == 0 && reinterpret_cast<uintptr_t>(p.D) % 16 == 0;
+        return true;
+    }
     // TMA: 16-byte aligned bases and row strides.
     if (p.K % 8 != 0) return false;
     if (!p.b_col_major && p.N % 8 != 0) return false;
@@ -370,7 +376,7 @@ const GemmConfig* choose_gemm_config(const GemmProblem& p) {
         double eff, slots;
         if (c.kind == GEMM_TC) { eff = c.bn == 256 ? 1.0 : c.bn == 128 ? 0.85 : 0.6; slots = sms; }
         else if (c.kind == GEMM_TC_PAIR) { eff = kPairEfficiency; slots = sms / 2; }
-        else { eff = (c.bm == 128 ? 1.0 : c.bm == 64 ? 0.8 : 0.55) / 24.0; slots = sms * (c.bm == 128 ? 2.0 : 4.0); }
+        else { eff = (c.bm == 128 ? 1.0 : c.bm == 64 ? 0.8 : c.bk == 32 ? 0.75 : 0.55) / 24.0; slots = sms * (c.bm == 128 ? 2.0 : 4.0); }
         const double waves = static_cast<double>(static_cast<long long>((tiles + slots - 1) / slots));
         const double cost = waves * c.bm * c.bn / eff;
         if (!best || cost < best_cost) { best = &c; best_cost = cost; }

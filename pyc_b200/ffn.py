@@ -30,8 +30,9 @@ def shard_weights(w1, s1, w2, rank, world, b1=None):
 class FfnBlock:
     """Device-resident shard of one FFN block plus its workspace; call run() once per step.
 
-    With more than one rank the tokens are processed in `chunks` row slices: the all-reduce of slice i runs on a second
-    stream while slice i+1 is still in its GEMMs, so only the last slice's collective is exposed."""
+    With more than one rank the tokens can be processed in `chunks` row slices: the all-reduce of slice i runs on a
+    second stream while slice i+1 is still in its GEMMs.  Measured on 2/4/8 B200s this loses to the unsliced block
+    (four times the launches, smaller GEMMs, one NCCL call per slice: 0.79 vs 0.64 ms at 2 ranks), so the default is 1."""
 
     def __init__(self, tokens, hidden, inner_local, w1, s1, w2, s2, torch, group=None, chunks=None):
         self.torch, self.group = torch, group
@@ -44,7 +45,7 @@ class FfnBlock:
         dist = torch.distributed
         self.parallel = group is not None or (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1)
         if chunks is None:
-            chunks = 4 if self.parallel and tokens % 4 == 0 and tokens // 4 >= 1024 else 1
+            chunks = 1
         if tokens % chunks:
             raise ValueError(f"{tokens} tokens do not split into {chunks} equal chunks")
         self.chunks, self.rows = chunks, tokens // chunks

@@ -27,7 +27,7 @@ def _dev(dtype, shape, seed, std):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "add", "bias_gelu", "layernorm", "softmax", "reduce_sum", "attention", "conv2d", "ffn", "gemm_fp8"])
+    ap.add_argument("op", choices=["gemm", "add", "bias_gelu", "layernorm", "softmax", "reduce_sum", "attention", "conv2d", "ffn", "gemm_fp8", "latency"])
     ap.add_argument("--dtype", default="bf16", choices=list(DT))
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=16384); ap.add_argument("--cols", type=int, default=8192)
@@ -66,6 +66,28 @@ def main():
                "reduce_sum": lambda: backend.reduce_sum(dt, X.data_ptr(), O.data_ptr(), a.rows, a.cols)}[a.op]
         nbytes = {"add": 3, "reduce_sum": 1}.get(a.op, 2) * n * es
         work = ("GB/s", nbytes / 1e9)
+    elif a.op == "latency":
+        # benchmark configuration 1: the 512^3 fp32 matmul -> add(bias) -> relu module through pyc_cuda_dispatch, device tensors;
+        # wall-clock per call (graph replay + stream sync), p50 / p95 over --iters calls
+        import time
+        from . import ir
+        x, w, b = workloads.gemm_inputs(1, a.m, a.k, a.n, ("uniform", -1.0, 1.0))
+        dev = [torch.from_numpy(t).cuda() for t in (x, w, b)]
+        out = torch.zeros((a.m, a.n), dtype=torch.float32, device="cuda")
+        host = [torch.from_numpy(t).pin_memory() for t in (x, w, b)]; hout = torch.zeros((a.m, a.n), dtype=torch.float32).pin_memory()
+        module = ir.matmul_bias_act(abi.DTYPE_F32, a.m, a.k, a.n, bias="row", act="relu")
+        def tens(ts, o):
+            return ([backend.make_tensor(t.data_ptr(), t.numel() * 4, abi.DTYPE_F32, tuple(t.shape)) for t in ts],
+                    [backend.make_tensor(o.data_ptr(), o.numel() * 4, abi.DTYPE_F32, (a.m, a.n))])
+        for label, (ins, outs) in (("device tensors", tens(dev, out)), ("pinned host tensors", tens(host, hout))):
+            for _ in range(20):
+                backend.dispatch(module, ins, outs)
+            ts = []
+            for _ in range(a.iters):
+                t0 = time.perf_counter(); st, trace = backend.dispatch(module, ins, outs); ts.append((time.perf_counter() - t0) * 1e6)
+            ts.sort()
+            print(f"latency f32 {a.m}x{a.k}x{a.n} {label}: p50 {ts[len(ts) // 2]:.1f} us  p95 {ts[int(len(ts) * 0.95)]:.1f} us  min {ts[0]:.1f} us  ({trace.reason.decode()})")
+        return
     elif a.op == "gemm_fp8":
         A = torch.randint(0, 120, (a.m, a.k), dtype=torch.uint8, device="cuda"); B = torch.randint(0, 120, (a.k, a.n), dtype=torch.uint8, device="cuda")
         rs = torch.ones(a.m, device="cuda"); cs = torch.ones(a.n, device="cuda"); D = torch.zeros((a.m, a.n), dtype=torch.int16, device="cuda")

@@ -88,6 +88,16 @@ def test_simt_f32(backend, oracle_lib, cfg):
     run_case(backend, oracle_lib, abi.DTYPE_F32, 130, 70, 100, cfg=cfg, b_col_major=True, seed=15)
 
 
+def test_simt_latency_tile_f32(backend, oracle_lib):
+    cfg = "simt_async_32x64x32"
+    run_case(backend, oracle_lib, abi.DTYPE_F32, 512, 512, 512, cfg=cfg, add_mode=abi.ADD_ROW_BIAS, act=abi.ACT_RELU, seed=21)
+    run_case(backend, oracle_lib, abi.DTYPE_F32, 100, 64, 72, cfg=cfg, add_mode=abi.ADD_MATRIX, act=abi.ACT_GELU, seed=22)
+    run_case(backend, oracle_lib, abi.DTYPE_F32, 33, 68, 20, cfg=cfg, add_mode=abi.ADD_SCALAR, seed=23)      # ragged tiles, K not a multiple of 32
+    run_case(backend, oracle_lib, abi.DTYPE_F32, 1, 4, 4, cfg=cfg, seed=24)
+    with pytest.raises(backend.BackendError):   # N % 4 != 0 is not this tile's business
+        run_case(backend, oracle_lib, abi.DTYPE_F32, 16, 16, 18, cfg=cfg, seed=25)
+
+
 def test_config1_f32_512_matches_golden_definition(backend, oracle_lib):
     # BASELINE config 1: X[512,512] W[512,512] b[512] ~ U(-1,1), matmul -> add -> relu.
     from gpu_util import empty_device, rel_err, sync_ok, to_device
