@@ -21,6 +21,7 @@
 #include <string.h>
 
 #include <chrono>
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -473,20 +474,25 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
     const unsigned skip_mask = (want_static && ctx->resident_base == base && ctx->last_base == base) ? want_static : 0u;
     const uint64_t key = base ^ (0x9e3779b97f4a7c15ull * (1 + pin_mask + 4 * skip_mask));
 
-    Plan plan;
-    {
+    // A key that already has a captured graph also has its plan: replays skip planning altogether.
+    std::shared_ptr<Plan> plan_holder;
+    if (replay_enabled) {
+        auto hit = ctx->graphs.find(key);
+        if (hit != ctx->graphs.end() && hit->second.plan) plan_holder = std::static_pointer_cast<Plan>(hit->second.plan);
+    }
+    if (!plan_holder) {
+        plan_holder = std::make_shared<Plan>();
         // The skip variant is planned with the same pinning so every offset matches the uploading variant.
-        Plan tmp;
-        const int rc = build_plan(module, inputs, n_in, outputs, n_out, in_mem, out_mem, skip_out, pin_mask, &tmp);
+        const int rc = build_plan(module, inputs, n_in, outputs, n_out, in_mem, out_mem, skip_out, pin_mask, plan_holder.get());
         if (rc != 0) { snprintf(reason, reason_size, rc > 0 ? "b200_unsupported_module" : "b200_bad_arguments"); return rc; }
-        plan = tmp;
         if (skip_mask) {
             std::vector<Step> kept;
-            for (const Step& s : plan.steps) if (!(s.kind == S_H2D && s.ext < 2 && (skip_mask & (1u << s.ext)))) kept.push_back(s);
-            plan.steps.swap(kept);
+            for (const Step& s : plan_holder->steps) if (!(s.kind == S_H2D && s.ext < 2 && (skip_mask & (1u << s.ext)))) kept.push_back(s);
+            plan_holder->steps.swap(kept);
         }
+        if (ctx->ensure_arena(plan_holder->arena_peak) != 0 || ctx->ensure_pinned(plan_holder->stage_bytes) != 0) { snprintf(reason, reason_size, "b200_out_of_memory"); return -1; }
     }
-    if (ctx->ensure_arena(plan.arena_peak) != 0 || ctx->ensure_pinned(plan.stage_bytes) != 0) { snprintf(reason, reason_size, "b200_out_of_memory"); return -1; }
+    Plan& plan = *plan_holder;
     ctx->last_plan_peak = plan.arena_peak;
 
     // Host -> pinned staging (outside the graph; PyC does the same at cuda_backend.c:551-650).
@@ -520,19 +526,11 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
             cudaGraphDestroy(graph);
             if (ie != cudaSuccess) { snprintf(reason, reason_size, "b200_graph_instantiate_failed:%s", cudaGetErrorString(ie)); cudaGetLastError(); return -1; }
             cg.kernels = kernels;
+            cg.plan = plan_holder;
             it = ctx->graphs.emplace(key, cg).first;
         } else {
             replayed = true;
             kernels = it->second.kernels;
-            // The symbol for the reason string: recompute the choice (cheap, no launch).
-            for (const Step& s : plan.steps)
-                if (s.kind == S_GEMM) {
-                    GemmProblem p; p.dtype = plan.values[resolve(plan.values, s.out)].dtype; p.M = s.M; p.N = s.N; p.K = s.K;
-                    p.A = value_ptr(plan, ctx, inputs, outputs, s.in0); p.B = value_ptr(plan, ctx, inputs, outputs, s.in1);
-                    const GemmConfig* cfg = choose_gemm_config(p);
-                    if (cfg) plan.symbol = gemm_symbol(p.dtype, *cfg);
-                    break;
-                }
         }
         if (cudaGraphLaunch(it->second.exec, launch_stream) != cudaSuccess) {
             snprintf(reason, reason_size, "b200_graph_launch_failed:%s", cudaGetErrorString(cudaGetLastError())); return -1;

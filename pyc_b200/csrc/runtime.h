@@ -5,6 +5,7 @@
 
 #include <cstdint>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -19,6 +20,7 @@ struct CachedGraph {
     cudaGraphExec_t exec = nullptr;
     size_t kernels = 0;
     size_t replays = 0;
+    std::shared_ptr<void> plan;   // the dispatch layer's step list for this key (opaque here)
 };
 
 struct DeviceContext {
