@@ -45,6 +45,14 @@ template <> struct AElem<0> {
     static __device__ __forceinline__ uint32_t pack(float a, float b) { __half2 p = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&p); }
 };
 
+// 2^x on the MUFU in one instruction (flush-to-zero; exp2f() adds range handling the softmax does not need:
+// arguments are <= 0 up to the lazy-rescale margin and -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct AttnParams {
     int seq, batch_heads, causal;
     float scale_log2;  // scale * log2(e)
@@ -296,7 +304,7 @@ struct AttnSmem2 {
     static constexpr int Q_BYTES = BQ * HD * 2;
     static constexpr int KV_TILE = BKV2 * HD * 2;      // one [64 x HD] tile
     static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = Q_BYTES + 2 * KV_TILE, BAR_OFF = Q_BYTES + 4 * KV_TILE;
-    static constexpr int NUM_BARS = 12;
+    static constexpr int NUM_BARS = 14;
     static constexpr size_t BYTES = 1024 + BAR_OFF + NUM_BARS * 8 + 16;
 };
 
@@ -321,7 +329,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + SM::NUM_BARS);
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 24, v_full = bar0 + 40, v_empty = bar0 + 56,
-                   s_full = bar0 + 72, p_full = bar0 + 88, pv_done = bar0 + 96;
+                   s_full = bar0 + 72, p_full = bar0 + 88, pv_done = bar0 + 104;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_qb = (ap.seq + BQ - 1) / BQ;
@@ -337,9 +345,8 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         for (int i = 0; i < 2; ++i) {
             mbar_init(k_full + 8 * i, 1); mbar_init(k_empty + 8 * i, 1);
             mbar_init(v_full + 8 * i, 1); mbar_init(v_empty + 8 * i, 1);
-            mbar_init(s_full + 8 * i, 1);
+            mbar_init(s_full + 8 * i, 1); mbar_init(p_full + 8 * i, 4);
         }
-        mbar_init(p_full, 4);
         mbar_init(pv_done, 1);
         fence_barrier_init();
         fence_proxy_async();
@@ -390,7 +397,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             for (int j = 0; j < nblk && ok; ++j) {
                 const int st = j & 1;
                 if (!mbar_wait(v_full + 8 * st, (j >> 1) & 1, status, 0x55)) { ok = false; break; }
-                if (!mbar_wait(p_full, j & 1, status, 0x56)) { ok = false; break; }
+                if (!mbar_wait(p_full + 8 * (j & 1), (j >> 1) & 1, status, 0x56)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t p_tmem = tmem_base + (j & 1) * BKV2;   // P_j sits where S_j was: 32 columns of packed pairs
 #pragma unroll
@@ -438,26 +445,30 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
             for (int t = 0; t < 32; ++t) m_blk = fmaxf(m_blk, fmaxf(__uint_as_float(r0[t]), __uint_as_float(r1[t])));
             m_blk *= ap.scale_log2;
+            // Lazy rescale: the reference maximum only moves when the new block exceeds it by more than 2^8; until then P is
+            // allowed to reach 256 (exact in bf16/f16 range, sums are fp32) and O needs no correction.
             const float m_new = fmaxf(m_run, m_blk);
-            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-            const float alpha = exp2f(m_run - m_use);
+            const bool move = m_new > m_run + 8.0f || m_run == -INFINITY;
+            const float m_ref = move ? m_new : m_run;
+            const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+            const float alpha = move ? fast_exp2(m_run - m_use) : 1.0f;   // m_run = -inf -> 0
             float l_blk = 0.0f;
             uint32_t packed[32];
 #pragma unroll
             for (int t = 0; t < 32; t += 2) {
-                const float a0 = exp2f(fmaf(__uint_as_float(r0[t]), ap.scale_log2, -m_use)), a1 = exp2f(fmaf(__uint_as_float(r0[t + 1]), ap.scale_log2, -m_use));
-                const float b0 = exp2f(fmaf(__uint_as_float(r1[t]), ap.scale_log2, -m_use)), b1 = exp2f(fmaf(__uint_as_float(r1[t + 1]), ap.scale_log2, -m_use));
+                const float a0 = fast_exp2(fmaf(__uint_as_float(r0[t]), ap.scale_log2, -m_use)), a1 = fast_exp2(fmaf(__uint_as_float(r0[t + 1]), ap.scale_log2, -m_use));
+                const float b0 = fast_exp2(fmaf(__uint_as_float(r1[t]), ap.scale_log2, -m_use)), b1 = fast_exp2(fmaf(__uint_as_float(r1[t + 1]), ap.scale_log2, -m_use));
                 l_blk += (a0 + a1) + (b0 + b1);
                 packed[t / 2] = E::pack(a0, a1);          // keys k0 + t, t+1      -> column t/2
                 packed[16 + t / 2] = E::pack(b0, b1);     // keys k0 + 32 + t, ..  -> column 16 + t/2
             }
             l_run = l_run * alpha + l_blk;
-            m_run = m_new;
-            // O is shared with the previous block's P*V: it must have finished before O is rescaled or P_j replaces S_j... (S_j itself
-            // was read above; P_{j-1} lives in the other buffer).
-            if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, status, 0x59)) { ok = false; break; }
-            tc_fence_after();
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+            m_run = m_ref;
+            // O is touched only when some row of this warp moved its reference maximum; only then must the previous P*V
+            // (which accumulates into O) have finished.  P_j itself goes into S_j's columns, which nothing else uses now.
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                if (!mbar_wait(pv_done, (j - 1) & 1, status, 0x59)) { ok = false; break; }
+                tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
                     uint32_t o[32];
@@ -472,7 +483,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(p_full + 8 * (j & 1));
         }
         if (ok && mbar_wait(pv_done, (nblk - 1) & 1, status, 0x5a)) {
             tc_fence_after();
