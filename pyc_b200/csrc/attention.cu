@@ -53,6 +53,20 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// 2^x on the FMA pipe for x <= 0 (Cody-Waite split + cubic on the fraction, relative error 7.5e-5, well inside what the
+// 16-bit P keeps).  The softmax is co-limited by the MUFU (16 exp2 per clock per SM), so a fixed share of the elements
+// takes this route instead.
+__device__ __forceinline__ float poly_exp2(float x) {
+    x = fmaxf(x, -126.0f);
+    const float magic = 12582912.0f;                 // 1.5 * 2^23: adding it rounds x to the nearest integer in the low mantissa bits
+    const float t = x + magic;
+    const float f = x - (t - magic);                 // fraction in [-0.5, 0.5]
+    float p = fmaf(0.05517165f, f, 0.24261113f);     // cubic fitted for minimum relative error of 2^f on [-0.5, 0.5]: 7.5e-5
+    p = fmaf(p, f, 0.69326097f);
+    p = fmaf(p, f, 0.99992806f);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));   // scale by 2^round(x): add to the exponent field
+}
+
 struct AttnParams {
     int seq, batch_heads, causal;
     float scale_log2;  // scale * log2(e)
@@ -308,7 +322,7 @@ struct AttnSmem2 {
     static constexpr size_t BYTES = 1024 + BAR_OFF + NUM_BARS * 8 + 16;
 };
 
-template <int HD, int FMT>
+template <int HD, int FMT, bool POLY>
 __global__ void __launch_bounds__(192, 2)
 attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, AttnParams ap, int* status) {
@@ -456,8 +470,11 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             uint32_t packed[32];
 #pragma unroll
             for (int t = 0; t < 32; t += 2) {
+                // one element in four goes to the FMA-pipe polynomial (compile-time pattern after unrolling)
                 const float a0 = fast_exp2(fmaf(__uint_as_float(r0[t]), ap.scale_log2, -m_use)), a1 = fast_exp2(fmaf(__uint_as_float(r0[t + 1]), ap.scale_log2, -m_use));
-                const float b0 = fast_exp2(fmaf(__uint_as_float(r1[t]), ap.scale_log2, -m_use)), b1 = fast_exp2(fmaf(__uint_as_float(r1[t + 1]), ap.scale_log2, -m_use));
+                const float b0 = fast_exp2(fmaf(__uint_as_float(r1[t]), ap.scale_log2, -m_use));
+                const float b1x = fmaf(__uint_as_float(r1[t + 1]), ap.scale_log2, -m_use);
+                const float b1 = POLY ? poly_exp2(b1x) : fast_exp2(b1x);
                 l_blk += (a0 + a1) + (b0 + b1);
                 packed[t / 2] = E::pack(a0, a1);          // keys k0 + t, t+1      -> column t/2
                 packed[16 + t / 2] = E::pack(b0, b1);     // keys k0 + 32 + t, ..  -> column 16 + t/2
@@ -606,15 +623,20 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
         }
         kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
     } else {
-        auto kernel = attention_tc2_kernel<HD, FMT>;
+        // PYC_B200_ATTENTION_POLY=0 keeps every exp2 on the MUFU.
+        const char* pe = getenv("PYC_B200_ATTENTION_POLY");
+        const bool poly = !(pe && pe[0] == '0');
         // Never less than 76 KB: at most two CTAs per SM, because each takes 256 of the 512 TMEM columns.
         constexpr size_t smem = AttnSmem2<HD>::BYTES > 76 * 1024 ? AttnSmem2<HD>::BYTES : 76 * 1024;
-        static bool attr_set2[16] = {};
-        if (dev < 16 && !attr_set2[dev]) {
-            B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-            attr_set2[dev] = true;
+        static bool attr_set2[16][2] = {};
+        auto k_poly = attention_tc2_kernel<HD, FMT, true>;
+        auto k_mufu = attention_tc2_kernel<HD, FMT, false>;
+        if (dev < 16 && !attr_set2[dev][poly]) {
+            B200_CUDA_OK(cudaFuncSetAttribute(poly ? k_poly : k_mufu, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            attr_set2[dev][poly] = true;
         }
-        kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
+        if (poly) k_poly<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
+        else k_mufu<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
     }
     B200_CUDA_OK(cudaGetLastError());
     count_launch();
