@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (N=1): BASELINE config 2 -- M=N=K=8192 bf16 ~N(0,1)*0.02, fp32
+Workload (N=1): benchmark configuration 2 -- M=N=K=8192 bf16 ~N(0,1)*0.02, fp32
 accumulate, bias[8192] + exact GELU epilogue, bf16 output -- as the IR module
 matmul -> add -> gelu run through pyc_cuda_dispatch.  A step is one run of that
 graph.  With N GPUs every rank runs its own independent graph (weak scaling, no

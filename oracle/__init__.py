@@ -28,7 +28,7 @@ F32, BF16, F16 = 0, 1, 2
 def build(ref_root=None):
     """Compile the restatement and, if a PyC checkout is present, PyC's own CPU runtime."""
     subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
-    ref_root = ref_root or "/root/reference"
+    ref_root = ref_root or os.environ.get("PYC_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
     if os.path.isdir(os.path.join(ref_root, "src", "compiler")):
         subprocess.run(["make", "-s", "-C", _HERE, "ref", f"REF={ref_root}"], check=True)
 

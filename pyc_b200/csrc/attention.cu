@@ -456,8 +456,15 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                     if (k0 + 32 + t >= k_lim) r1[t] = 0xff800000u;
                 }
             }
+            {   // four independent chains instead of one 64-deep dependency
+                float mx[4] = {m_blk, m_blk, m_blk, m_blk};
 #pragma unroll
-            for (int t = 0; t < 32; ++t) m_blk = fmaxf(m_blk, fmaxf(__uint_as_float(r0[t]), __uint_as_float(r1[t])));
+                for (int t = 0; t < 32; t += 4) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], fmaxf(__uint_as_float(r0[t + u]), __uint_as_float(r1[t + u])));
+                }
+                m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            }
             m_blk *= ap.scale_log2;
             // Lazy rescale: the reference maximum only moves when the new block exceeds it by more than 2^8; until then P is
             // allowed to reach 256 (exact in bf16/f16 range, sums are fp32) and O needs no correction.
@@ -466,7 +473,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             const float m_ref = move ? m_new : m_run;
             const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
             const float alpha = move ? fast_exp2(m_run - m_use) : 1.0f;   // m_run = -inf -> 0
-            float l_blk = 0.0f;
+            float l_part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t packed[32];
 #pragma unroll
             for (int t = 0; t < 32; t += 2) {
@@ -475,11 +482,11 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 const float b0 = fast_exp2(fmaf(__uint_as_float(r1[t]), ap.scale_log2, -m_use));
                 const float b1x = fmaf(__uint_as_float(r1[t + 1]), ap.scale_log2, -m_use);
                 const float b1 = POLY ? poly_exp2(b1x) : fast_exp2(b1x);
-                l_blk += (a0 + a1) + (b0 + b1);
+                l_part[(t >> 1) & 3] += (a0 + a1) + (b0 + b1);
                 packed[t / 2] = E::pack(a0, a1);          // keys k0 + t, t+1      -> column t/2
                 packed[16 + t / 2] = E::pack(b0, b1);     // keys k0 + 32 + t, ..  -> column 16 + t/2
             }
-            l_run = l_run * alpha + l_blk;
+            l_run = l_run * alpha + ((l_part[0] + l_part[1]) + (l_part[2] + l_part[3]));
             m_run = m_ref;
             // O is touched only when some row of this warp moved its reference maximum; only then must the previous P*V
             // (which accumulates into O) have finished.  P_j itself goes into S_j's columns, which nothing else uses now.
@@ -623,9 +630,10 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
         }
         kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
     } else {
-        // PYC_B200_ATTENTION_POLY=0 keeps every exp2 on the MUFU.
+        // PYC_B200_ATTENTION_POLY=1 moves a quarter of the exp2 work to the FMA pipe (measured slightly slower on B200: the
+        // softmax warps are bound by their dependency chains, not by the MUFU; kept as a switch).
         const char* pe = getenv("PYC_B200_ATTENTION_POLY");
-        const bool poly = !(pe && pe[0] == '0');
+        const bool poly = pe && pe[0] == '1';
         // Never less than 76 KB: at most two CTAs per SM, because each takes 256 of the 512 TMEM columns.
         constexpr size_t smem = AttnSmem2<HD>::BYTES > 76 * 1024 ? AttnSmem2<HD>::BYTES : 76 * 1024;
         static bool attr_set2[16][2] = {};

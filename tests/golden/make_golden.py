@@ -1,6 +1,6 @@
 """Regenerate tests/golden/ref_cpu_cases.npz from PyC's own CPU executor.
 
-Needs a PyC checkout (default /root/reference) and `make -C oracle ref`.  Each
+Needs a PyC checkout (PYC_REFERENCE_DIR, default: a `reference` directory next to this repository) and `make -C oracle ref`.  Each
 case is a small IR module run through pyc_compile_model / pyc_run_model of the
 UNMODIFIED PyC sources with backend CPU, fusion off, fp32 tensors and the bias
 materialised to [M,N] (PyC's CPU ADD has no broadcast,

@@ -55,7 +55,7 @@ def test_conv_direct_paths_and_legacy_symbols(backend, oracle_lib):
 
 
 def test_conv_full_size_configs_sampled_images(backend, oracle_lib):
-    # BASELINE config 4 at full size; the oracle checks the first, a middle and the last image (images are independent).
+    # benchmark configuration 4 at full size; the oracle checks the first, a middle and the last image (images are independent).
     from gpu_util import empty_device, rel_err, round_to, sync_ok, to_device, to_host_f32
     for (N, H, C, K) in [(64, 56, 64, 64), (256, 14, 256, 256)]:
         x_s, x_r = round_to(abi.DTYPE_BF16, workloads.uniform((N, H, H, C), workloads.tensor_seed(4, 0)))
@@ -116,7 +116,7 @@ def test_attention_row_warp_paths(backend, oracle_lib):
 
 
 def test_attention_config3_shape_sampled_heads(backend, oracle_lib):
-    # BASELINE config 3: 8 x 32 heads, seq 2048, d 128, causal.  All 256 heads run; the oracle checks three of them
+    # benchmark configuration 3: 8 x 32 heads, seq 2048, d 128, causal.  All 256 heads run; the oracle checks three of them
     # (heads are independent), and every row of every head must be a convex combination of V rows (|out| <= max|V|).
     import torch
     from gpu_util import rel_err, sync_ok, to_device, to_host_f32

@@ -99,7 +99,7 @@ def test_simt_latency_tile_f32(backend, oracle_lib):
 
 
 def test_config1_f32_512_matches_golden_definition(backend, oracle_lib):
-    # BASELINE config 1: X[512,512] W[512,512] b[512] ~ U(-1,1), matmul -> add -> relu.
+    # benchmark configuration 1: X[512,512] W[512,512] b[512] ~ U(-1,1), matmul -> add -> relu.
     from gpu_util import empty_device, rel_err, sync_ok, to_device
     x, w, b = workloads.gemm_inputs(1, 512, 512, 512, ("uniform", -1.0, 1.0))
     want = oracle_lib.relu(oracle_lib.add(oracle_lib.matmul(x, w), b))
@@ -126,7 +126,7 @@ def test_legacy_symbols_and_beta(backend, oracle_lib):
 
 
 def test_full_size_8192_spot_rows_and_linearity(backend, oracle_lib):
-    # BASELINE config 2 at full size: sampled rows against the oracle, plus a size-independent property
+    # benchmark configuration 2 at full size: sampled rows against the oracle, plus a size-independent property
     # (GEMM is linear in alpha; bias+GELU epilogue applied to the same accumulators).
     import torch
     from gpu_util import rel_err, sync_ok, to_device, to_host_f32

@@ -24,7 +24,7 @@ def front():
 
 @pytest.mark.parametrize("bias,act", [("row", "relu"), (None, None), ("matrix", "relu")])
 def test_pyc_run_model_on_cuda_backend_f32(front, oracle_lib, bias, act):
-    M, K, N = 512, 512, 512   # BASELINE config 1 shape
+    M, K, N = 512, 512, 512   # benchmark configuration 1 shape
     x, w, b = workloads.gemm_inputs(1, M, K, N, ("uniform", -1.0, 1.0))
     if bias == "matrix":
         b = workloads.uniform((M, N), 77)
