@@ -317,15 +317,13 @@ template <int HD>
 struct AttnSmem2 {
     static constexpr int Q_BYTES = BQ * HD * 2;
     static constexpr int KV_TILE = BKV2 * HD * 2;      // one [64 x HD] tile
-    static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = Q_BYTES + 2 * KV_TILE, XCH_OFF = Q_BYTES + 4 * KV_TILE;
-    static constexpr int XCH_BYTES = 2 * 2 * BQ * 4;
-    static constexpr int BAR_OFF = XCH_OFF + XCH_BYTES;
-    static constexpr int NUM_BARS = 18;
+    static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = Q_BYTES + 2 * KV_TILE, BAR_OFF = Q_BYTES + 4 * KV_TILE;
+    static constexpr int NUM_BARS = 14;
     static constexpr size_t BYTES = 1024 + BAR_OFF + NUM_BARS * 8 + 16;
 };
 
 template <int HD, int FMT, bool POLY>
-__global__ void __launch_bounds__(320, 2)
+__global__ void __launch_bounds__(192, 2)
 attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, AttnParams ap, int* status) {
     using SM = AttnSmem2<HD>;
@@ -345,8 +343,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + SM::NUM_BARS);
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 24, v_full = bar0 + 40, v_empty = bar0 + 56,
-                   s_full = bar0 + 72, p_full = bar0 + 88, pv_done = bar0 + 104, xbar = bar0 + 112;
-    float* xch = reinterpret_cast<float*>(smem + SM::XCH_OFF);   // [2 slots][2 halves][128 rows] row maxima / sums handed between the two warps of a row
+                   s_full = bar0 + 72, p_full = bar0 + 88, pv_done = bar0 + 104;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_qb = (ap.seq + BQ - 1) / BQ;
@@ -362,10 +359,9 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         for (int i = 0; i < 2; ++i) {
             mbar_init(k_full + 8 * i, 1); mbar_init(k_empty + 8 * i, 1);
             mbar_init(v_full + 8 * i, 1); mbar_init(v_empty + 8 * i, 1);
-            mbar_init(s_full + 8 * i, 1); mbar_init(p_full + 8 * i, 8);
+            mbar_init(s_full + 8 * i, 1); mbar_init(p_full + 8 * i, 4);
         }
         mbar_init(pv_done, 1);
-        for (int i = 0; i < 4; ++i) mbar_init(xbar + 8 * i, 2);
         fence_barrier_init();
         fence_proxy_async();
     }
@@ -433,108 +429,94 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             }
         }
     } else {
-        // Eight softmax warps: warps w and w+4 share the 32 rows of TMEM lane quarter w % 4 and take 32 of the block's 64
-        // keys each (more independent instruction streams per scheduler than one warp per quarter).  Per block they
-        // hand each other their row maxima through shared memory (bounded mbarrier wait, no named barrier); row sums
-        // stay private until the end.
         const int wq = warp & 3;
-        const int half = (warp - 2) >> 2;                 // which 32 keys of the block / which half of O's columns
         const int row = wq * 32 + lane;
         const int qi = q0 + row;
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(wq * 32) << 16);
-        const uint32_t my_xbar = xbar + 8 * wq;
-        uint32_t xphase = 0;
         float m_run = -INFINITY, l_run = 0.0f;
         bool ok = true;
         int k_lim = ap.seq;
         if (ap.causal) k_lim = min(k_lim, qi + 1);
-        constexpr int OC = HD / 2;                        // O columns owned by this warp
         for (int j = 0; j < nblk && ok; ++j) {
             const uint32_t s_addr = lane_addr + (j & 1) * BKV2;
             if (!mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1, status, 0x58)) { ok = false; break; }
             tc_fence_after();
-            const int k0 = j * BKV2 + half * 32;
-            uint32_t r0[32];
-            tmem_ld_32x32(s_addr + half * 32, r0);
+            const int k0 = j * BKV2;
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(s_addr, r0);
+            tmem_ld_32x32(s_addr + 32, r1);
             tmem_ld_wait();
             // only blocks that touch the diagonal or the end of the sequence need per-element masking (warp-uniform test)
-            const bool masked = (k0 + 32 > ap.seq) || (ap.causal && k0 + 32 > q0 + wq * 32 + 1);
+            const bool masked = (k0 + BKV2 > ap.seq) || (ap.causal && k0 + BKV2 > q0 + wq * 32 + 1);
+            float m_blk = -INFINITY;
             if (masked) {
 #pragma unroll
-                for (int t = 0; t < 32; ++t) if (k0 + t >= k_lim) r0[t] = 0xff800000u;   // -inf
+                for (int t = 0; t < 32; ++t) {
+                    if (k0 + t >= k_lim) r0[t] = 0xff800000u;       // -inf
+                    if (k0 + 32 + t >= k_lim) r1[t] = 0xff800000u;
+                }
             }
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            {   // four independent chains instead of one 64-deep dependency
+                float mx[4] = {m_blk, m_blk, m_blk, m_blk};
 #pragma unroll
-            for (int t = 0; t < 32; t += 4) {
+                for (int t = 0; t < 32; t += 4) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], __uint_as_float(r0[t + u]));
+                    for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], fmaxf(__uint_as_float(r0[t + u]), __uint_as_float(r1[t + u])));
+                }
+                m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             }
-            float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            // exchange with the warp that holds the other 32 keys of these rows
-            float* slot = xch + (j & 1) * 256;
-            slot[half * 128 + row] = m_blk;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(my_xbar);
-            if (!mbar_wait(my_xbar, xphase, status, 0x5b)) { ok = false; break; }
-            xphase ^= 1;
-            m_blk = fmaxf(m_blk, slot[(half ^ 1) * 128 + row]) * ap.scale_log2;
+            m_blk *= ap.scale_log2;
             // Lazy rescale: the reference maximum only moves when the new block exceeds it by more than 2^8; until then P is
-            // allowed to reach 256 (16-bit P keeps its relative precision, sums are fp32) and O needs no correction.
+            // allowed to reach 256 (exact in bf16/f16 range, sums are fp32) and O needs no correction.
             const float m_new = fmaxf(m_run, m_blk);
             const bool move = m_new > m_run + 8.0f || m_run == -INFINITY;
             const float m_ref = move ? m_new : m_run;
             const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
             const float alpha = move ? fast_exp2(m_run - m_use) : 1.0f;   // m_run = -inf -> 0
             float l_part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t packed[16];
+            uint32_t packed[32];
 #pragma unroll
             for (int t = 0; t < 32; t += 2) {
-                const float a0 = fast_exp2(fmaf(__uint_as_float(r0[t]), ap.scale_log2, -m_use));
-                const float a1x = fmaf(__uint_as_float(r0[t + 1]), ap.scale_log2, -m_use);
-                const float a1 = (POLY && (t & 2)) ? poly_exp2(a1x) : fast_exp2(a1x);   // POLY: one element in four on the FMA pipe
-                l_part[(t >> 1) & 3] += a0 + a1;
-                packed[t / 2] = E::pack(a0, a1);          // keys k0 + t, t+1 -> column half*16 + t/2
+                // one element in four goes to the FMA-pipe polynomial (compile-time pattern after unrolling)
+                const float a0 = fast_exp2(fmaf(__uint_as_float(r0[t]), ap.scale_log2, -m_use)), a1 = fast_exp2(fmaf(__uint_as_float(r0[t + 1]), ap.scale_log2, -m_use));
+                const float b0 = fast_exp2(fmaf(__uint_as_float(r1[t]), ap.scale_log2, -m_use));
+                const float b1x = fmaf(__uint_as_float(r1[t + 1]), ap.scale_log2, -m_use);
+                const float b1 = POLY ? poly_exp2(b1x) : fast_exp2(b1x);
+                l_part[(t >> 1) & 3] += (a0 + a1) + (b0 + b1);
+                packed[t / 2] = E::pack(a0, a1);          // keys k0 + t, t+1      -> column t/2
+                packed[16 + t / 2] = E::pack(b0, b1);     // keys k0 + 32 + t, ..  -> column 16 + t/2
             }
             l_run = l_run * alpha + ((l_part[0] + l_part[1]) + (l_part[2] + l_part[3]));
             m_run = m_ref;
-            // O is touched only when some row moved its reference maximum (both warps of a quarter see the same rows, so
-            // they agree); only then must the previous P*V, which accumulates into O, have finished.
+            // O is touched only when some row of this warp moved its reference maximum; only then must the previous P*V
+            // (which accumulates into O) have finished.  P_j itself goes into S_j's columns, which nothing else uses now.
             if (j > 0 && __any_sync(0xffffffffu, move)) {
                 if (!mbar_wait(pv_done, (j - 1) & 1, status, 0x59)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < OC / 32; ++c) {
+                for (int c = 0; c < HD / 32; ++c) {
                     uint32_t o[32];
-                    tmem_ld_32x32(lane_addr + O_COL + half * OC + c * 32, o);
+                    tmem_ld_32x32(lane_addr + O_COL + c * 32, o);
                     tmem_ld_wait();
 #pragma unroll
                     for (int t = 0; t < 32; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * alpha);
-                    tmem_st_32x32(lane_addr + O_COL + half * OC + c * 32, o);
+                    tmem_st_32x32(lane_addr + O_COL + c * 32, o);
                 }
             }
-            tmem_st_32x16(s_addr + half * 16, packed);
+            tmem_st_32x32(s_addr, packed);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + 8 * (j & 1));
         }
-        // row sums of the two halves meet here
-        if (ok) {
-            float* slot = xch + (nblk & 1) * 256;
-            slot[half * 128 + row] = l_run;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(my_xbar);
-            ok = mbar_wait(my_xbar, xphase, status, 0x5c);
-            if (ok) l_run += slot[(half ^ 1) * 128 + row];
-        }
         if (ok && mbar_wait(pv_done, (nblk - 1) & 1, status, 0x5a)) {
             tc_fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            T* orow = reinterpret_cast<T*>(ap.out) + (static_cast<size_t>(bh) * ap.seq + qi) * HD + half * OC;
+            T* orow = reinterpret_cast<T*>(ap.out) + (static_cast<size_t>(bh) * ap.seq + qi) * HD;
 #pragma unroll 1
-            for (int c = 0; c < OC / 32; ++c) {
+            for (int c = 0; c < HD / 32; ++c) {
                 uint32_t r[32];
-                tmem_ld_32x32(lane_addr + O_COL + half * OC + c * 32, r);
+                tmem_ld_32x32(lane_addr + O_COL + c * 32, r);
                 tmem_ld_wait();
                 if (qi < ap.seq) {
                     uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
@@ -661,8 +643,8 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
             B200_CUDA_OK(cudaFuncSetAttribute(poly ? k_poly : k_mufu, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
             attr_set2[dev][poly] = true;
         }
-        if (poly) k_poly<<<grid, 320, smem, stream>>>(tq, tk, tv, ap, status);
-        else k_mufu<<<grid, 320, smem, stream>>>(tq, tk, tv, ap, status);
+        if (poly) k_poly<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
+        else k_mufu<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
     }
     B200_CUDA_OK(cudaGetLastError());
     count_launch();
