@@ -491,6 +491,15 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
             plan_holder->steps.swap(kept);
         }
         if (ctx->ensure_arena(plan_holder->arena_peak) != 0 || ctx->ensure_pinned(plan_holder->stage_bytes) != 0) { snprintf(reason, reason_size, "b200_out_of_memory"); return -1; }
+        // PYC_B200_AUTOTUNE=1: the first time a GEMM shape is planned, time its tile configurations (outside any capture)
+        // and let the measured winner, not the shape heuristic, go into the graph.  Timings also reach PyC's registry.
+        if (env_true("PYC_B200_AUTOTUNE")) {
+            for (const Step& st : plan_holder->steps)
+                if (st.kind == S_GEMM) {
+                    const pyc_dtype dt = plan_holder->values[resolve(plan_holder->values, st.out)].dtype;
+                    if (!has_gemm_winner(dt, st.M, st.N, st.K)) autotune_gemm_unlocked(ctx, dt, st.M, st.N, st.K, 3, nullptr, nullptr);
+                }
+        }
     }
     Plan& plan = *plan_holder;
     ctx->last_plan_peak = plan.arena_peak;

@@ -395,6 +395,61 @@ int launch_gemm(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream
     return launch_gemm_simt(cfg, p, stream);
 }
 
+bool has_gemm_winner(pyc_dtype dtype, int M, int N, int K) {
+    std::lock_guard<std::mutex> lk(g_win_mu);
+    return g_winners.count(std::make_tuple(static_cast<int>(dtype), M, N, K)) != 0;
+}
+
+// Times every tile configuration that supports (dtype, M, N, K) on the context's stream with CUDA events and remembers
+// the fastest.  The caller holds ctx->mu.  Must not be called while a stream capture is open (it allocates and synchronises).
+int autotune_gemm_unlocked(DeviceContext* ctx, pyc_dtype dtype, int M, int N, int K, int iters, std::string* best_symbol, double* best_ms) {
+    if (!ctx || M <= 0 || N <= 0 || K <= 0) return -1;
+    if (iters < 1) iters = 3;
+    const size_t es = dtype_size(dtype);
+    if (!es) { set_error("autotune: unsupported dtype"); return -1; }
+    void *A = nullptr, *B = nullptr, *D = nullptr;
+    if (cudaMalloc(&A, es * M * K) != cudaSuccess || cudaMalloc(&B, es * K * N) != cudaSuccess || cudaMalloc(&D, es * M * N) != cudaSuccess) {
+        cudaGetLastError(); cudaFree(A); cudaFree(B); cudaFree(D); set_error("autotune: out of device memory"); return -1;
+    }
+    cudaMemset(A, 0, es * M * K); cudaMemset(B, 0, es * K * N);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    GemmProblem p;
+    p.dtype = dtype; p.M = M; p.N = N; p.K = K; p.A = A; p.B = B; p.D = D;
+    int timed = 0;
+    const GemmConfig* best = nullptr;
+    double best_t = 0.0;
+    int n = 0;
+    const GemmConfig* cfgs = gemm_configs(&n);
+    for (int i = 0; i < n; ++i) {
+        if (!gemm_config_supports(cfgs[i], p)) continue;
+        // The SIMT tiles are only worth timing for fp32 or when no tensor-core tile fits.
+        if (cfgs[i].kind == GEMM_SIMT && dtype != PYC_DTYPE_F32 && best) continue;
+        if (launch_gemm(cfgs[i], p, ctx->stream) != 0) continue;  // warm-up
+        double t = 1e30;
+        for (int it = 0; it < iters; ++it) {
+            cudaEventRecord(e0, ctx->stream);
+            launch_gemm(cfgs[i], p, ctx->stream);
+            cudaEventRecord(e1, ctx->stream);
+            if (cudaEventSynchronize(e1) != cudaSuccess) { t = 1e30; break; }
+            float ms = 0.0f;
+            cudaEventElapsedTime(&ms, e0, e1);
+            if (ms < t) t = ms;
+        }
+        if (t >= 1e30) continue;
+        registry_report_ms("matmul", gemm_symbol(dtype, cfgs[i]).c_str(), t);
+        ++timed;
+        if (!best || t < best_t) { best = &cfgs[i]; best_t = t; }
+    }
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaFree(A); cudaFree(B); cudaFree(D);
+    if (!best) { set_error("autotune: no configuration ran"); return -1; }
+    remember_gemm_winner(dtype, M, N, K, best);
+    if (best_symbol) *best_symbol = gemm_symbol(dtype, *best);
+    if (best_ms) *best_ms = best_t;
+    return timed;
+}
+
 }  // namespace b200
 
 // ======================================================================== C API
@@ -472,52 +527,15 @@ int pyc_b200_reduce_sum(pyc_dtype dtype, const void* x, void* out, size_t rows, 
 
 int pyc_b200_autotune_gemm(pyc_dtype dtype, int M, int N, int K, int iters, char* best_symbol, size_t best_symbol_size, double* best_ms) {
     DeviceContext* ctx = current_context();
-    if (!ctx || M <= 0 || N <= 0 || K <= 0) return -1;
-    if (iters < 1) iters = 3;
-    const size_t es = dtype_size(dtype);
-    if (!es) { set_error("autotune: unsupported dtype"); return -1; }
-    void *A = nullptr, *B = nullptr, *D = nullptr;
-    if (cudaMalloc(&A, es * M * K) != cudaSuccess || cudaMalloc(&B, es * K * N) != cudaSuccess || cudaMalloc(&D, es * M * N) != cudaSuccess) {
-        cudaGetLastError(); cudaFree(A); cudaFree(B); cudaFree(D); set_error("autotune: out of device memory"); return -1;
-    }
-    cudaMemset(A, 0, es * M * K); cudaMemset(B, 0, es * K * N);
-    cudaEvent_t e0, e1;
-    cudaEventCreate(&e0); cudaEventCreate(&e1);
-    GemmProblem p;
-    p.dtype = dtype; p.M = M; p.N = N; p.K = K; p.A = A; p.B = B; p.D = D;
-    int timed = 0;
-    const GemmConfig* best = nullptr;
-    double best_t = 0.0;
-    int n = 0;
-    const GemmConfig* cfgs = gemm_configs(&n);
+    if (!ctx) return -1;
     std::lock_guard<std::mutex> lk(ctx->mu);
-    for (int i = 0; i < n; ++i) {
-        if (!gemm_config_supports(cfgs[i], p)) continue;
-        // The SIMT tiles are only worth timing for fp32 or when no tensor-core tile fits.
-        if (cfgs[i].kind == GEMM_SIMT && dtype != PYC_DTYPE_F32 && best) continue;
-        if (launch_gemm(cfgs[i], p, ctx->stream) != 0) continue;  // warm-up
-        double t = 1e30;
-        for (int it = 0; it < iters; ++it) {
-            cudaEventRecord(e0, ctx->stream);
-            launch_gemm(cfgs[i], p, ctx->stream);
-            cudaEventRecord(e1, ctx->stream);
-            if (cudaEventSynchronize(e1) != cudaSuccess) { t = 1e30; break; }
-            float ms = 0.0f;
-            cudaEventElapsedTime(&ms, e0, e1);
-            if (ms < t) t = ms;
-        }
-        if (t >= 1e30) continue;
-        registry_report_ms("matmul", gemm_symbol(dtype, cfgs[i]).c_str(), t);
-        ++timed;
-        if (!best || t < best_t) { best = &cfgs[i]; best_t = t; }
-    }
-    cudaEventDestroy(e0); cudaEventDestroy(e1);
-    cudaFree(A); cudaFree(B); cudaFree(D);
-    if (!best) { set_error("autotune: no configuration ran"); return -1; }
-    remember_gemm_winner(dtype, M, N, K, best);
-    if (best_symbol && best_symbol_size) { strncpy(best_symbol, gemm_symbol(dtype, *best).c_str(), best_symbol_size - 1); best_symbol[best_symbol_size - 1] = 0; }
-    if (best_ms) *best_ms = best_t;
-    return timed;
+    std::string best;
+    double ms = 0.0;
+    const int n = autotune_gemm_unlocked(ctx, dtype, M, N, K, iters, &best, &ms);
+    if (n < 0) return -1;
+    if (best_symbol && best_symbol_size) { strncpy(best_symbol, best.c_str(), best_symbol_size - 1); best_symbol[best_symbol_size - 1] = 0; }
+    if (best_ms) *best_ms = ms;
+    return n;
 }
 
 int pyc_b200_get_runtime_info(pyc_b200_runtime_info* out) {

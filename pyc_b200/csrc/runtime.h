@@ -52,5 +52,7 @@ struct DeviceContext {
 
 DeviceContext* current_context();
 std::string gemm_symbol(pyc_dtype d, const GemmConfig& c);
+bool has_gemm_winner(pyc_dtype dtype, int M, int N, int K);
+int autotune_gemm_unlocked(DeviceContext* ctx, pyc_dtype dtype, int M, int N, int K, int iters, std::string* best_symbol, double* best_ms);
 
 }  // namespace b200

@@ -152,3 +152,17 @@ def test_hardware_family_and_autotune_feed_registry(backend):
     assert backend.load().pyc_cuda_current_hardware_family() == 3  # B200 reports PyC's highest family (hopper)
     sym, ms, n = backend.autotune_gemm(abi.DTYPE_BF16, 1024, 1024, 1024, iters=3)
     assert sym.startswith("b200_gemm_bf16_tc_") and ms > 0 and n >= 3
+
+
+def test_dispatch_autotunes_on_first_sight_when_asked(backend, oracle_lib, monkeypatch):
+    # PYC_B200_AUTOTUNE=1: the tile configuration that goes into the graph is the measured winner for this shape
+    from gpu_util import rel_err
+    monkeypatch.setenv("PYC_B200_AUTOTUNE", "1")
+    M, K, N = 768, 1024, 1280
+    mod = ir.matmul_bias_act(abi.DTYPE_BF16, M, K, N, bias="row", act="relu")
+    arrays = [workloads.normal((M, K), 111, 0.5), workloads.normal((K, N), 112, 0.5), workloads.normal((N,), 113, 2.0)]
+    got, want, trace = run_module_both(backend, oracle_lib, mod, arrays, abi.DTYPE_BF16, (M, N), True)
+    assert rel_err(got, want) <= 2e-2
+    assert "b200_gemm_bf16_tc" in trace.reason.decode()
+    sym, ms, n = backend.autotune_gemm(abi.DTYPE_BF16, M, N, K, iters=2)   # same shape again: consistent answer format
+    assert sym.startswith("b200_gemm_bf16_") and n >= 4
