@@ -154,7 +154,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t fb = full0 + 8 * stage;
                     mbar_arrive_expect_tx(fb, STAGE_TX);
                     const uint32_t adst = smem_u32(sA + stage * A_STAGE_BYTES), bdst = smem_u32(sB + stage * B_STAGE_BYTES);
-                    if (ep.l2_hints) {
+                    if (ep.l2_hints == 1 || ep.l2_hints == 2) {
                         tma_load_2d_hint(adst, &tmA, fb, kb * BK, m0, pol_a);
                         if (B_KMAJOR) {
                             tma_load_2d_hint(bdst, &tmB, fb, kb * BK, n0, pol_b);

@@ -3,7 +3,7 @@
 // interface as gemm_tc.cu; what changes is the data movement per SM:
 //   * a pair owns a 256 x 256 output tile; CTA r keeps rows r*128..+127 in its TMEM
 //   * per k-block each CTA loads its own A rows (128 x 64) and only HALF of the B tile
-//     (64 x 128), 32 KB instead of 48 KB, so the ring is 6 deep instead of 4 and the
+//     (64 x 128), 32 KB instead of 48 KB, so the ring is 7 deep instead of 4 and the
 //     B traffic per SM is halved
 //   * loads of both CTAs are counted on the leader's (even CTA's) "full" barrier; the
 //     leader's single MMA thread issues for the pair and commits completion to the
@@ -266,8 +266,8 @@ int launch_pair_instance(const GemmProblem& p, cudaStream_t stream, int* status)
 int launch_gemm_tc_pair(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream, int* status) {
     (void)cfg;
     const bool bf16 = p.dtype == PYC_DTYPE_BF16;
-    if (p.b_col_major) return bf16 ? launch_pair_instance<6, true, 1>(p, stream, status) : launch_pair_instance<6, true, 0>(p, stream, status);
-    return bf16 ? launch_pair_instance<6, false, 1>(p, stream, status) : launch_pair_instance<6, false, 0>(p, stream, status);
+    if (p.b_col_major) return bf16 ? launch_pair_instance<7, true, 1>(p, stream, status) : launch_pair_instance<7, true, 0>(p, stream, status);
+    return bf16 ? launch_pair_instance<7, false, 1>(p, stream, status) : launch_pair_instance<7, false, 0>(p, stream, status);
 }
 
 }  // namespace b200
