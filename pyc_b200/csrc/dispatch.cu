@@ -22,6 +22,7 @@
 
 #include <chrono>
 #include <memory>
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -100,6 +101,8 @@ struct Plan {
     size_t arena_peak = 0, arena_total = 0, stage_bytes = 0;
     std::string symbol;          // GEMM configuration of the first matmul (for the reason string)
     bool all_device = true;
+    // Host-tensor pipeline (see plan_pipeline): index of the GEMM step, rows per chunk, chunk count.
+    int pipe_gemm = -1, pipe_rows = 0, pipe_chunks = 0;
 };
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -359,6 +362,38 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
     return 0;
 }
 
+// A call whose tensors live in pinned host memory is bound by the PCIe copies, not by the kernel: for the
+// common shape "upload operands, one (fused) GEMM, download the result" the rows of A are uploaded in chunks,
+// each chunk's GEMM starts as soon as its rows have landed, and its rows of the result go back while the next
+// chunk is still arriving.  Uploads, kernels and downloads sit on three streams joined by events, so the same
+// enqueue works under stream capture (the graph gets three parallel branches) and on a plain stream.
+// Recognised here; anything else keeps the serial order.
+void plan_pipeline(Plan* plan) {
+    plan->pipe_gemm = -1;
+    const std::vector<Step>& S = plan->steps;
+    int g = -1;
+    for (size_t i = 0; i < S.size(); ++i)
+        if (S[i].kind == S_GEMM) { if (g >= 0) return; g = static_cast<int>(i); }
+    if (g < 0 || g + 2 != static_cast<int>(S.size())) return;
+    const Step& gemm = S[g];
+    const Step& down = S[g + 1];
+    const int a = resolve(plan->values, gemm.in0), d = resolve(plan->values, gemm.out);
+    if (down.kind != S_D2H || down.via_stage || resolve(plan->values, down.in0) != d) return;
+    if (resolve(plan->values, gemm.in1) == a || (gemm.in2 >= 0 && resolve(plan->values, gemm.in2) == a)) return;
+    bool a_uploaded = false;
+    for (int i = 0; i < g; ++i) {
+        if (S[i].kind != S_H2D) return;
+        if (resolve(plan->values, S[i].out) == a) { if (S[i].via_stage) return; a_uploaded = true; }
+    }
+    if (!a_uploaded) return;
+    const size_t moved = plan->values[a].bytes + plan->values[d].bytes;
+    if (gemm.M < 1024 || moved < (size_t(32) << 20)) return;
+    int rows = (gemm.M / 8 + 255) / 256 * 256;      // whole 256-row tiles, about eight chunks
+    plan->pipe_gemm = g;
+    plan->pipe_rows = rows;
+    plan->pipe_chunks = (gemm.M + rows - 1) / rows;
+}
+
 void* value_ptr(const Plan& plan, const DeviceContext* ctx, const pyc_tensor* inputs, pyc_tensor* outputs, int id) {
     id = resolve(plan.values, id);
     const Value& v = plan.values[id];
@@ -370,9 +405,67 @@ void* value_ptr(const Plan& plan, const DeviceContext* ctx, const pyc_tensor* in
     }
 }
 
+// The pipelined order of plan_pipeline().  Every side stream is forked from and joined back into `stream`.
+int enqueue_pipelined(Plan& plan, DeviceContext* ctx, const pyc_tensor* inputs, pyc_tensor* outputs, cudaStream_t stream, size_t* kernels) {
+    const Step& gemm = plan.steps[plan.pipe_gemm];
+    const Step& down = plan.steps[plan.pipe_gemm + 1];
+    const int chunks = plan.pipe_chunks, rows = plan.pipe_rows;
+    if (ctx->ensure_pipeline(static_cast<size_t>(2 * chunks + 3)) != 0) return -1;
+    cudaEvent_t* ev = ctx->events.data();   // 0 fork, 1 shared operands landed, 2 downloads done, 3.. A chunks, 3+chunks.. D chunks
+    const int a_id = resolve(plan.values, gemm.in0);
+    const pyc_dtype dt = plan.values[resolve(plan.values, gemm.out)].dtype;
+    const size_t es = dtype_size(dt);
+    B200_CUDA_OK(cudaEventRecord(ev[0], stream));
+    B200_CUDA_OK(cudaStreamWaitEvent(ctx->copy_in, ev[0], 0));
+    B200_CUDA_OK(cudaStreamWaitEvent(ctx->copy_out, ev[0], 0));
+    const char* a_host = nullptr;
+    for (int i = 0; i < plan.pipe_gemm; ++i) {
+        const Step& s = plan.steps[i];
+        if (resolve(plan.values, s.out) == a_id) { a_host = static_cast<const char*>(inputs[s.ext].data); continue; }
+        const void* src = s.via_stage ? static_cast<const void*>(static_cast<char*>(ctx->pinned) + s.stage_off) : inputs[s.ext].data;
+        B200_CUDA_OK(cudaMemcpyAsync(value_ptr(plan, ctx, inputs, outputs, s.out), src, s.bytes, cudaMemcpyHostToDevice, ctx->copy_in));
+    }
+    B200_CUDA_OK(cudaEventRecord(ev[1], ctx->copy_in));
+    B200_CUDA_OK(cudaStreamWaitEvent(stream, ev[1], 0));
+    char* a_dev = static_cast<char*>(value_ptr(plan, ctx, inputs, outputs, gemm.in0));
+    char* d_dev = static_cast<char*>(value_ptr(plan, ctx, inputs, outputs, gemm.out));
+    char* d_host = static_cast<char*>(outputs[down.ext].data);
+    const char* add = gemm.in2 >= 0 ? static_cast<const char*>(value_ptr(plan, ctx, inputs, outputs, gemm.in2)) : nullptr;
+    for (int c = 0; c < chunks; ++c) {
+        const size_t r0 = static_cast<size_t>(c) * rows;
+        const size_t rc = std::min<size_t>(rows, gemm.M - r0);
+        const size_t a_off = r0 * gemm.K * es, d_off = r0 * gemm.N * es;
+        B200_CUDA_OK(cudaMemcpyAsync(a_dev + a_off, a_host + a_off, rc * gemm.K * es, cudaMemcpyHostToDevice, ctx->copy_in));
+        B200_CUDA_OK(cudaEventRecord(ev[3 + c], ctx->copy_in));
+        B200_CUDA_OK(cudaStreamWaitEvent(stream, ev[3 + c], 0));
+        GemmProblem p;
+        p.dtype = dt;
+        p.M = static_cast<int>(rc); p.N = gemm.N; p.K = gemm.K;
+        p.A = a_dev + a_off; p.B = value_ptr(plan, ctx, inputs, outputs, gemm.in1); p.D = d_dev + d_off;
+        p.add_mode = gemm.add_mode; p.act = gemm.act;
+        p.add = add ? (gemm.add_mode == PYC_B200_ADD_MATRIX ? add + d_off : add) : nullptr;
+        const GemmConfig* cfg = choose_gemm_config(p);
+        if (!cfg) { set_error("no GEMM configuration for %zux%dx%d", rc, gemm.N, gemm.K); return -1; }
+        if (plan.symbol.empty()) plan.symbol = gemm_symbol(dt, *cfg);
+        if (launch_gemm(*cfg, p, stream) != 0) return -1;
+        ++*kernels;
+        B200_CUDA_OK(cudaEventRecord(ev[3 + chunks + c], stream));
+        B200_CUDA_OK(cudaStreamWaitEvent(ctx->copy_out, ev[3 + chunks + c], 0));
+        B200_CUDA_OK(cudaMemcpyAsync(d_host + d_off, d_dev + d_off, rc * gemm.N * es, cudaMemcpyDeviceToHost, ctx->copy_out));
+    }
+    B200_CUDA_OK(cudaEventRecord(ev[2], ctx->copy_out));
+    B200_CUDA_OK(cudaStreamWaitEvent(stream, ev[2], 0));
+    return 0;
+}
+
 // Enqueue every step on `stream` (which may be capturing).
 int enqueue_plan(Plan& plan, DeviceContext* ctx, const pyc_tensor* inputs, pyc_tensor* outputs, cudaStream_t stream, size_t* kernels) {
     *kernels = 0;
+    if (plan.pipe_gemm >= 0) {
+        if (enqueue_pipelined(plan, ctx, inputs, outputs, stream, kernels) != 0) return -1;
+        B200_CUDA_OK(cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, stream));
+        return 0;
+    }
     for (const Step& s : plan.steps) {
         switch (s.kind) {
             case S_H2D: {
@@ -462,6 +555,9 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
     for (size_t i = 0; i < n_in; ++i) { base = fnv1a(base, &inputs[i].data, sizeof(void*)); base = fnv1a(base, &inputs[i].size_bytes, sizeof(size_t)); base = fnv1a(base, &in_mem[i], sizeof(MemKind)); }
     for (size_t i = 0; i < n_out; ++i) { base = fnv1a(base, &outputs[i].data, sizeof(void*)); base = fnv1a(base, &outputs[i].size_bytes, sizeof(size_t)); base = fnv1a(base, &out_mem[i], sizeof(MemKind)); }
     base = fnv1a(base, &skip_out, sizeof(skip_out));
+    // PYC_B200_PIPELINE_HOST_COPIES=0 keeps uploads, kernel and downloads strictly one after another.
+    const bool pipeline_enabled = env_default_true("PYC_B200_PIPELINE_HOST_COPIES");
+    base = fnv1a(base, &pipeline_enabled, sizeof(pipeline_enabled));
 
     // PYC_CUDA_ASSUME_STATIC_LHS/RHS (cuda_backend.c:2521-2522, 2625-2636): once a host operand has
     // been uploaded for this module and nothing else used the arena since, do not upload it again.
@@ -490,6 +586,7 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
             for (const Step& s : plan_holder->steps) if (!(s.kind == S_H2D && s.ext < 2 && (skip_mask & (1u << s.ext)))) kept.push_back(s);
             plan_holder->steps.swap(kept);
         }
+        if (pipeline_enabled) plan_pipeline(plan_holder.get());
         if (ctx->ensure_arena(plan_holder->arena_peak) != 0 || ctx->ensure_pinned(plan_holder->stage_bytes) != 0) { snprintf(reason, reason_size, "b200_out_of_memory"); return -1; }
         // PYC_B200_AUTOTUNE=1: the first time a GEMM shape is planned, time its tile configurations (outside any capture)
         // and let the measured winner, not the shape heuristic, go into the graph.  Timings also reach PyC's registry.

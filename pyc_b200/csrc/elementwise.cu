@@ -54,9 +54,10 @@ __device__ __forceinline__ void store_vec(T* p, const float (&f)[VEC]) {
     }
 }
 
-__device__ __forceinline__ float act_fn(float v, int act) {
-    if (act == PYC_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
-    if (act == PYC_B200_ACT_GELU) return gelu_erf(v);
+template <int ACT>
+__device__ __forceinline__ float act_fn(float v) {
+    if constexpr (ACT == PYC_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
+    if constexpr (ACT == PYC_B200_ACT_GELU) return gelu_erf(v);
     return v;
 }
 
@@ -83,8 +84,8 @@ __global__ void __launch_bounds__(256) add_kernel(const T* __restrict__ a, const
 }
 
 // --------------------------------------------------------- bias + activation --
-template <typename T, int VEC>
-__global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, const T* __restrict__ add, int add_mode, int act,
+template <typename T, int VEC, int ACT>
+__global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, const T* __restrict__ add, int add_mode,
                                                       T* __restrict__ out, size_t nvec, size_t cols) {
     const float sadd = add_mode == PYC_B200_ADD_SCALAR ? to_f(add[0]) : 0.0f;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
@@ -108,7 +109,7 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, 
                 for (int j = 0; j < VEC; ++j) v[u][j] += y[j];
             }
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) v[u][j] = act_fn(v[u][j] + sadd, act);
+            for (int j = 0; j < VEC; ++j) v[u][j] = act_fn<ACT>(v[u][j] + sadd);
             store_vec<T, VEC>(out + i * VEC, v[u]);
         }
     }
@@ -116,8 +117,8 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, 
 
 // Row bias (+ activation): every thread owns one 16-byte column slot, keeps its slice of the bias in registers and
 // walks down the rows, so there is no index arithmetic beyond one add per row.
-template <typename T, int VEC>
-__global__ void __launch_bounds__(256) row_bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, int act, T* __restrict__ out,
+template <typename T, int VEC, int ACT>
+__global__ void __launch_bounds__(256) row_bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ out,
                                                           size_t rows, size_t cols) {
     const size_t vec_per_row = cols / VEC;
     const size_t col_vec = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(256) row_bias_act_kernel(const T* __restrict__
             const size_t r = r0 + static_cast<size_t>(u) * gridDim.y;
             if (r >= rows) continue;
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) v[u][j] = act_fn(v[u][j] + b[j], act);
+            for (int j = 0; j < VEC; ++j) v[u][j] = act_fn<ACT>(v[u][j] + b[j]);
             store_vec<T, VEC>(out + r * cols + col_vec * VEC, v[u]);
         }
     }
@@ -273,19 +274,28 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
             const float dmean = s * inv_n;
             const float mean = pivot + dmean;
             const float rstd = rsqrtf(fmaxf(ss * inv_n - dmean * dmean, 0.0f) + eps);
-            for_each([&](float (&f)[VEC], size_t vi) {
-                float g[VEC], b[VEC];
-                if (gamma) load_vec<T, VEC>(gamma + vi * VEC, g);
-                if (beta) load_vec<T, VEC>(beta + vi * VEC, b);
+            const float shift = -mean * rstd;   // y = x * rstd + shift: one FMA per element
+            if (gamma || beta) {                // block-uniform: the affine form pays for its loads only when asked
+                for_each([&](float (&f)[VEC], size_t vi) {
+                    float g[VEC], b[VEC];
+                    if (gamma) load_vec<T, VEC>(gamma + vi * VEC, g);
+                    if (beta) load_vec<T, VEC>(beta + vi * VEC, b);
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) {
-                    float y = (f[j] - mean) * rstd;
-                    if (gamma) y *= g[j];
-                    if (beta) y += b[j];
-                    f[j] = y;
-                }
-                store_vec<T, VEC>(orow + vi * VEC, f);
-            });
+                    for (int j = 0; j < VEC; ++j) {
+                        float y = fmaf(f[j], rstd, shift);
+                        if (gamma) y *= g[j];
+                        if (beta) y += b[j];
+                        f[j] = y;
+                    }
+                    store_vec<T, VEC>(orow + vi * VEC, f);
+                });
+            } else {
+                for_each([&](float (&f)[VEC], size_t vi) {
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) f[j] = fmaf(f[j], rstd, shift);
+                    store_vec<T, VEC>(orow + vi * VEC, f);
+                });
+            }
         } else {  // softmax
             float mx = -INFINITY;
             for_each([&](float (&f)[VEC], size_t) {
@@ -293,17 +303,43 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
                 for (int j = 0; j < VEC; ++j) mx = fmaxf(mx, f[j]);
             });
             mx = block_max<THREADS>(mx, scratch);
+            // exp(x - max) = 2^(x*log2e - max*log2e): one FMA + one MUFU op per element
+            const float l2e = 1.4426950408889634f, mshift = -mx * l2e;
             float den = 0.0f;
-            for_each([&](float (&f)[VEC], size_t) {
+            if constexpr (CACHED && VPT * VEC * (sizeof(T) == 4 ? 2 : 1) <= 32) {
+                float e[NV][VEC];   // the exponentials are computed once and kept for the normalising pass (when they fit in registers)
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) den += __expf(f[j] - mx);
-            });
-            const float inv = 1.0f / block_sum<THREADS>(den, scratch);
-            for_each([&](float (&f)[VEC], size_t vi) {
+                for (int i = 0; i < VPT; ++i) {
+                    const size_t vi = tid + static_cast<size_t>(i) * THREADS;
+                    if (vi < nvec) {
+                        float f[VEC];
+                        widen<T, VEC>(raw[i], f);
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) f[j] = __expf(f[j] - mx) * inv;
-                store_vec<T, VEC>(orow + vi * VEC, f);
-            });
+                        for (int j = 0; j < VEC; ++j) { e[i][j] = exp2f(fmaf(f[j], l2e, mshift)); den += e[i][j]; }
+                    }
+                }
+                const float inv = 1.0f / block_sum<THREADS>(den, scratch);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const size_t vi = tid + static_cast<size_t>(i) * THREADS;
+                    if (vi < nvec) {
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) e[i][j] *= inv;
+                        store_vec<T, VEC>(orow + vi * VEC, e[i]);
+                    }
+                }
+            } else {
+                for_each([&](float (&f)[VEC], size_t) {
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) den += exp2f(fmaf(f[j], l2e, mshift));
+                });
+                const float inv = 1.0f / block_sum<THREADS>(den, scratch);
+                for_each([&](float (&f)[VEC], size_t vi) {
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) f[j] = exp2f(fmaf(f[j], l2e, mshift)) * inv;
+                    store_vec<T, VEC>(orow + vi * VEC, f);
+                });
+            }
         }
     }
 }
@@ -371,8 +407,8 @@ int launch_add_typed(const void* a, const void* b, void* out, size_t n, cudaStre
     return 0;
 }
 
-template <typename T>
-int launch_bias_act_typed(const void* x, const void* add, int add_mode, int act, void* out, size_t rows, size_t cols, cudaStream_t s) {
+template <typename T, int ACT>
+int launch_bias_act_typed(const void* x, const void* add, int add_mode, void* out, size_t rows, size_t cols, cudaStream_t s) {
     constexpr int V = VecInfo<T>::N;
     const size_t n = rows * cols;
     if (!add) add_mode = PYC_B200_ADD_NONE;
@@ -383,12 +419,12 @@ int launch_bias_act_typed(const void* x, const void* add, int add_mode, int act,
         size_t gy = (static_cast<size_t>(sm_count()) * 8 * 256 / threads + gx - 1) / gx;  // fill every SM's thread slots
         if (gy > rows) gy = rows;
         if (gy > 65535) gy = 65535;
-        row_bias_act_kernel<T, V><<<dim3(gx, static_cast<unsigned>(gy)), threads, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add), act,
+        row_bias_act_kernel<T, V, ACT><<<dim3(gx, static_cast<unsigned>(gy)), threads, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add),
                                                                                       static_cast<T*>(out), rows, cols);
     } else if (cols % V == 0 && aligned16(x) && aligned16(out) && (add_mode == PYC_B200_ADD_SCALAR || aligned16(add))) {
-        bias_act_kernel<T, V><<<flat_grid(n / V, 256), 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add), add_mode, act, static_cast<T*>(out), n / V, cols);
+        bias_act_kernel<T, V, ACT><<<flat_grid(n / V, 256), 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add), add_mode, static_cast<T*>(out), n / V, cols);
     } else {
-        bias_act_kernel<T, 1><<<flat_grid(n, 256), 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add), add_mode, act, static_cast<T*>(out), n, cols);
+        bias_act_kernel<T, 1, ACT><<<flat_grid(n, 256), 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(add), add_mode, static_cast<T*>(out), n, cols);
     }
     B200_CUDA_OK(cudaGetLastError());
     count_launch();
@@ -409,12 +445,18 @@ int launch_add(pyc_dtype dt, const void* a, const void* b, void* out, size_t n, 
 
 int launch_bias_act(pyc_dtype dt, const void* x, const void* add, int add_mode, int act, void* out, size_t rows, size_t cols, cudaStream_t s) {
     if (rows == 0 || cols == 0) { set_error("bias_act: empty"); return -1; }
+    if (act != PYC_B200_ACT_NONE && act != PYC_B200_ACT_RELU && act != PYC_B200_ACT_GELU) { set_error("bias_act: unknown activation %d", act); return -1; }
+#define B200_BIAS_ACT(T)                                                                                          \
+    (act == PYC_B200_ACT_GELU   ? launch_bias_act_typed<T, PYC_B200_ACT_GELU>(x, add, add_mode, out, rows, cols, s) \
+     : act == PYC_B200_ACT_RELU ? launch_bias_act_typed<T, PYC_B200_ACT_RELU>(x, add, add_mode, out, rows, cols, s) \
+                                : launch_bias_act_typed<T, PYC_B200_ACT_NONE>(x, add, add_mode, out, rows, cols, s))
     switch (dt) {
-        case PYC_DTYPE_F32: return launch_bias_act_typed<float>(x, add, add_mode, act, out, rows, cols, s);
-        case PYC_DTYPE_BF16: return launch_bias_act_typed<__nv_bfloat16>(x, add, add_mode, act, out, rows, cols, s);
-        case PYC_DTYPE_F16: return launch_bias_act_typed<__half>(x, add, add_mode, act, out, rows, cols, s);
+        case PYC_DTYPE_F32: return B200_BIAS_ACT(float);
+        case PYC_DTYPE_BF16: return B200_BIAS_ACT(__nv_bfloat16);
+        case PYC_DTYPE_F16: return B200_BIAS_ACT(__half);
         default: set_error("bias_act: unsupported dtype %d", static_cast<int>(dt)); return -1;
     }
+#undef B200_BIAS_ACT
 }
 
 int launch_layernorm(pyc_dtype dt, const void* x, const void* gamma, const void* beta, void* out, size_t rows, size_t cols, float eps, cudaStream_t s) {

@@ -125,6 +125,16 @@ int DeviceContext::ensure_pinned(size_t bytes) {
     pinned_bytes = want;
     return 0;
 }
+int DeviceContext::ensure_pipeline(size_t event_count) {
+    if (!copy_in) B200_CUDA_OK(cudaStreamCreateWithFlags(&copy_in, cudaStreamNonBlocking));
+    if (!copy_out) B200_CUDA_OK(cudaStreamCreateWithFlags(&copy_out, cudaStreamNonBlocking));
+    while (events.size() < event_count) {
+        cudaEvent_t e = nullptr;
+        B200_CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        events.push_back(e);
+    }
+    return 0;
+}
 void DeviceContext::drop_graphs() {
     for (auto& kv : graphs) {
         if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
@@ -587,6 +597,9 @@ void pyc_b200_shutdown(void) {
     if (c->pinned) cudaFreeHost(c->pinned);
     if (c->status_dev) cudaFree(c->status_dev);
     if (c->status_host) cudaFreeHost(c->status_host);
+    for (cudaEvent_t e : c->events) cudaEventDestroy(e);
+    if (c->copy_in) cudaStreamDestroy(c->copy_in);
+    if (c->copy_out) cudaStreamDestroy(c->copy_out);
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }

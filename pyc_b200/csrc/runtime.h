@@ -38,6 +38,9 @@ struct DeviceContext {
     size_t arena_bytes = 0;
     void* pinned = nullptr;        // host staging for host-pointer tensors
     size_t pinned_bytes = 0;
+    // Side streams + events for the host-tensor pipeline (uploads, kernels and downloads of one call overlap).
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    std::vector<cudaEvent_t> events;
     std::map<uint64_t, CachedGraph> graphs;
     size_t graph_replays = 0;
     uint64_t last_base = 0;      // module+descriptor hash of the previous run
@@ -46,6 +49,7 @@ struct DeviceContext {
 
     int ensure_arena(size_t bytes);
     int ensure_pinned(size_t bytes);
+    int ensure_pipeline(size_t event_count);
     void drop_graphs();
     cudaStream_t active_stream() const { return use_user_stream ? user_stream : stream; }
 };

@@ -166,3 +166,59 @@ def test_dispatch_autotunes_on_first_sight_when_asked(backend, oracle_lib, monke
     assert "b200_gemm_bf16_tc" in trace.reason.decode()
     sym, ms, n = backend.autotune_gemm(abi.DTYPE_BF16, M, N, K, iters=2)   # same shape again: consistent answer format
     assert sym.startswith("b200_gemm_bf16_") and n >= 4
+
+
+def test_pinned_host_tensors_take_the_pipelined_path_and_match(backend, oracle_lib):
+    # Large pinned host operands: A goes up in row chunks, each chunk's GEMM and download overlap the next upload.
+    # Ragged on purpose (2100 rows = four 512-row chunks + 52).  Checked against the serial order of the same
+    # call (PYC_B200_PIPELINE_HOST_COPIES=0), against the oracle on rows around every chunk edge, under graph
+    # capture, graph replay (with new A contents) and on a plain stream.
+    import torch
+    M, K, N = 2100, 4096, 4096
+    dtype = abi.DTYPE_BF16
+    mod = ir.matmul_bias_act(dtype, M, K, N, bias="row", act="gelu")
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).pin_memory()
+    a_bits = [workloads.to_bf16_bits(workloads.normal((M, K), 300 + i)) for i in range(2)]
+    b_bits = workloads.to_bf16_bits(workloads.normal((K, N), 310) * np.float32(K ** -0.5))
+    bias_bits = workloads.to_bf16_bits(workloads.normal((N,), 311))
+    A, B, bias = pin(a_bits[0]), pin(b_bits), pin(bias_bits)
+    out = torch.zeros((M, N), dtype=torch.int16).pin_memory()
+    T = lambda t, shape: backend.make_tensor(t.data_ptr(), t.numel() * 2, dtype, shape)
+    ins, outs = [T(A, (M, K)), T(B, (K, N)), T(bias, (N,))], [T(out, (M, N))]
+    rows = sorted(set(list(range(0, 8)) + [r for e in (512, 1024, 1536, 2048) for r in range(e - 4, e + 4)] + list(range(M - 8, M))))
+    b_f32, bias_f32 = workloads.bf16_bits_to_f32(b_bits), workloads.bf16_bits_to_f32(bias_bits)
+
+    def check(which):
+        got = workloads.bf16_bits_to_f32(out.numpy().view(np.uint16)[rows])
+        a_f32 = workloads.bf16_bits_to_f32(a_bits[which][rows])
+        want = oracle_lib.gelu(oracle_lib.add(oracle_lib.matmul(a_f32, b_f32), bias_f32))
+        err = np.abs(got - want).max() / np.abs(want).max()
+        assert err < 2e-2, err   # bf16 storage tolerance
+
+    results = {}
+    try:
+        for mode, env in (("serial", {"PYC_B200_PIPELINE_HOST_COPIES": "0"}), ("pipelined", {}),
+                          ("pipelined_stream", {"PYC_CUDA_ENABLE_GRAPH_REPLAY": "0"})):
+            os.environ.update(env)
+            for run in range(2 if mode == "pipelined" else 1):
+                A.numpy()[:] = a_bits[run].view(np.int16)
+                out.zero_()
+                st, trace = backend.dispatch(mod, ins, outs)
+                assert st == abi.DISPATCH_OK and trace.fallback_to_cpu == 0
+                check(run)
+                results[(mode, run)] = out.numpy().copy()
+                if mode == "pipelined":
+                    assert trace.graph_replayed == run
+                    assert backend.runtime_info().kernels_per_graph == 5   # one GEMM per chunk
+                if mode == "serial":
+                    assert backend.runtime_info().kernels_per_graph == 1
+            for k in env:
+                os.environ.pop(k, None)
+    finally:
+        for k in ("PYC_B200_PIPELINE_HOST_COPIES", "PYC_CUDA_ENABLE_GRAPH_REPLAY"):
+            os.environ.pop(k, None)
+    # chunking only changes which CTA computes a row, not the arithmetic of the row
+    serial = workloads.bf16_bits_to_f32(results[("serial", 0)].view(np.uint16))
+    for key in (("pipelined", 0), ("pipelined_stream", 0)):
+        piped = workloads.bf16_bits_to_f32(results[key].view(np.uint16))
+        assert np.abs(piped - serial).max() <= 2e-2 * np.abs(serial).max()
