@@ -61,6 +61,18 @@ __device__ __forceinline__ float act_fn(float v) {
     return v;
 }
 
+// Activation over a register vector; GELU takes the elements two at a time (packed fp32 pairs).
+template <int ACT, int VEC>
+__device__ __forceinline__ void act_vec(float (&v)[VEC]) {
+    if constexpr (ACT == PYC_B200_ACT_GELU && VEC % 2 == 0) {
+#pragma unroll
+        for (int j = 0; j < VEC; j += 2) gelu_erf_x2(v[j], v[j + 1]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) v[j] = act_fn<ACT>(v[j]);
+    }
+}
+
 // ------------------------------------------------------------------ add ------
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t nvec) {
@@ -109,7 +121,8 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, 
                 for (int j = 0; j < VEC; ++j) v[u][j] += y[j];
             }
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) v[u][j] = act_fn<ACT>(v[u][j] + sadd);
+            for (int j = 0; j < VEC; ++j) v[u][j] += sadd;
+            act_vec<ACT, VEC>(v[u]);
             store_vec<T, VEC>(out + i * VEC, v[u]);
         }
     }
@@ -138,7 +151,8 @@ __global__ void __launch_bounds__(256) row_bias_act_kernel(const T* __restrict__
             const size_t r = r0 + static_cast<size_t>(u) * gridDim.y;
             if (r >= rows) continue;
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) v[u][j] = act_fn<ACT>(v[u][j] + b[j]);
+            for (int j = 0; j < VEC; ++j) v[u][j] += b[j];
+            act_vec<ACT, VEC>(v[u]);
             store_vec<T, VEC>(out + r * cols + col_vec * VEC, v[u]);
         }
     }

@@ -141,7 +141,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+            const uint32_t a_dst0 = smem_u32(sA), b_dst0 = smem_u32(sB);
+            uint32_t stage = 0, phase = 0, adst = a_dst0, bdst = b_dst0;
             bool ok = true;
             const uint64_t pol_a = l2_policy_evict_last();
             const uint64_t pol_b = ep.l2_hints == 2 ? l2_policy_evict_last() : l2_policy_evict_first();
@@ -153,7 +154,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, status, 1)) { ok = false; break; }
                     const uint32_t fb = full0 + 8 * stage;
                     mbar_arrive_expect_tx(fb, STAGE_TX);
-                    const uint32_t adst = smem_u32(sA + stage * A_STAGE_BYTES), bdst = smem_u32(sB + stage * B_STAGE_BYTES);
                     if (ep.l2_hints == 1 || ep.l2_hints == 2) {
                         tma_load_2d_hint(adst, &tmA, fb, kb * BK, m0, pol_a);
                         if (B_KMAJOR) {
@@ -171,13 +171,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             for (int j = 0; j < BN / 64; ++j) tma_load_2d(bdst + j * (BK * 128), &tmB, fb, n0 + j * 64, kb * BK);
                         }
                     }
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    adst += A_STAGE_BYTES; bdst += B_STAGE_BYTES;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; adst = a_dst0; bdst = b_dst0; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+            // This loop has to come round once per k-block of tensor-pipe time while sharing its scheduler with an
+            // epilogue warp: descriptor high words are constants and the low words are stepped, not rebuilt.
+            constexpr uint32_t DESC_HI = smem_desc_hi_sw128(1024);
+            constexpr uint32_t A_STEP = A_STAGE_BYTES >> 4, B_STEP = B_STAGE_BYTES >> 4;
+            constexpr uint32_t A_K16 = 32 >> 4, B_K16 = (B_KMAJOR ? 32 : 2048) >> 4;
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(sA), 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(sB), B_KMAJOR ? 16 : BK * 128);
+            uint32_t stage = 0, phase = 0, a_lo = a_lo0, b_lo = b_lo0;
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
@@ -188,23 +196,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(full0 + 8 * stage, phase, status, 3)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES);
-                    const uint32_t b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+                    umma_f16(d_tmem, smem_desc_join(a_lo, DESC_HI), smem_desc_join(b_lo, DESC_HI), IDESC, kb != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k4 = 0; k4 < BK / 16; ++k4) {
-                        const uint64_t adesc = make_smem_desc_sw128(a_base + k4 * 32, 16, 1024);
-                        const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_base + k4 * 32, 16, 1024)
-                                                        : make_smem_desc_sw128(b_base + k4 * 2048, BK * 128, 1024);
-                        umma_f16(d_tmem, adesc, bdesc, IDESC, (kb | k4) != 0 ? 1u : 0u);
-                    }
+                    for (uint32_t k4 = 1; k4 < BK / 16; ++k4)
+                        umma_f16(d_tmem, smem_desc_join(a_lo + k4 * A_K16, DESC_HI), smem_desc_join(b_lo + k4 * B_K16, DESC_HI), IDESC, 1u);
                     umma_commit(empty0 + 8 * stage);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    a_lo += A_STEP; b_lo += B_STEP;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
                 }
                 if (ok) umma_commit(tfull0 + 8 * acc);
             }
         }
     } else {
         const int wq = warp & 3;  // TMEM lane quarter this warp may read
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(wq * 32) << 16);
+        const T* addp = reinterpret_cast<const T*>(ep.add);
+        const float scalar_add = ep.add_mode == PYC_B200_ADD_SCALAR ? ep.add_scale * E::to_f(addp[0]) : 0.0f;
         int it = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
@@ -215,21 +222,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase, status, 4)) break;
             tc_fence_after();
             T* drow = reinterpret_cast<T*>(ep.D) + static_cast<size_t>(row) * N;
-            const T* addp = reinterpret_cast<const T*>(ep.add);
-            float scalar_add = 0.0f;
-            if (ep.add_mode == PYC_B200_ADD_SCALAR) scalar_add = ep.add_scale * E::to_f(addp[0]);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * BN + c * 32, r);
-                tmem_ld_wait();
-                const int col0 = n0 + c * 32;
-                if (col0 >= N) continue;
+            const uint32_t acc_addr = lane_base + acc * BN;
+            // One 32-column chunk: scale, add, activation, 64 bytes out.  The next chunk's TMEM load is already in flight.
+            auto chunk = [&](const uint32_t (&r)[32], int c) {
+                const int col0 = n0 + c * 32;  // warp-uniform
+                if (col0 >= N || row >= M) return;
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = ep.alpha * __uint_as_float(r[j]) + scalar_add;
                 const bool full_chunk = ep.vec_ok && (col0 + 32 <= N);
-                if (ep.add_mode == PYC_B200_ADD_ROW_BIAS || (ep.add_mode == PYC_B200_ADD_MATRIX && row < M)) {
+                if (ep.add_mode == PYC_B200_ADD_ROW_BIAS || ep.add_mode == PYC_B200_ADD_MATRIX) {
                     const T* src = ep.add_mode == PYC_B200_ADD_ROW_BIAS ? addp + col0 : addp + static_cast<size_t>(row) * N + col0;
                     if (full_chunk) {
 #pragma unroll
@@ -246,25 +248,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             if (col0 + j < N) v[j] += ep.add_scale * E::to_f(src[j]);
                     }
                 }
+                if (ep.act == PYC_B200_ACT_GELU) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], ep.act);
-                if (row < M) {
-                    if (full_chunk) {
-                        uint4* dst = reinterpret_cast<uint4*>(drow + col0);
+                    for (int j = 0; j < 32; j += 2) gelu_erf_x2(v[j], v[j + 1]);
+                } else if (ep.act == PYC_B200_ACT_RELU) {
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint4 u;
-                            u.x = E::pack(v[q * 8 + 0], v[q * 8 + 1]);
-                            u.y = E::pack(v[q * 8 + 2], v[q * 8 + 3]);
-                            u.z = E::pack(v[q * 8 + 4], v[q * 8 + 5]);
-                            u.w = E::pack(v[q * 8 + 6], v[q * 8 + 7]);
-                            dst[q] = u;
-                        }
-                    } else {
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) drow[col0 + j] = E::from_f(v[j]);
-                    }
+                    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
                 }
+                if (full_chunk) {
+                    uint4* dst = reinterpret_cast<uint4*>(drow + col0);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint4 u;
+                        u.x = E::pack(v[q * 8 + 0], v[q * 8 + 1]);
+                        u.y = E::pack(v[q * 8 + 2], v[q * 8 + 3]);
+                        u.z = E::pack(v[q * 8 + 4], v[q * 8 + 5]);
+                        u.w = E::pack(v[q * 8 + 6], v[q * 8 + 7]);
+                        dst[q] = u;
+                    }
+                } else {
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < N) drow[col0 + j] = E::from_f(v[j]);
+                }
+            };
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(acc_addr, r0);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c += 2) {
+                tmem_ld_wait();
+                tmem_ld_32x32(acc_addr + (c + 1) * 32, r1);
+                chunk(r0, c);
+                __syncwarp();
+                tmem_ld_wait();
+                if (c + 2 < BN / 32) tmem_ld_32x32(acc_addr + (c + 2) * 32, r0);
+                chunk(r1, c + 1);
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();

@@ -100,34 +100,46 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
+    // The two single-thread loops below share their scheduler with an epilogue warp each, and the MMA loop has to come
+    // round once per 512 tensor-pipe cycles; everything that does not change per k-block (peer barrier addresses,
+    // descriptor high words, shared-memory bases) is therefore computed once, and the per-stage values are stepped
+    // with one add each instead of being rebuilt.
     if (warp == 0) {
         if (lane == 0) {  // each CTA loads its own halves; bytes are counted on the leader's barrier
-            uint32_t stage = 0, phase = 0;
+            const uint32_t leader_full0 = map_to_cta(full0, 0);
+            const uint32_t a_dst0 = smem_u32(sA), b_dst0 = smem_u32(sB);
+            uint32_t stage = 0, phase = 0, a_dst = a_dst0, b_dst = b_dst0;
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
                 int tm, tn;
                 pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
                 const int m0 = tm * 2 * BM + static_cast<int>(rank) * BM;
                 const int n0 = tn * BN + static_cast<int>(rank) * BNH;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = 0, k0 = 0; kb < num_kb; ++kb, k0 += BK) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, status, 0x41)) { ok = false; break; }
-                    const uint32_t leader_full = map_to_cta(full0 + 8 * stage, 0);
+                    const uint32_t leader_full = leader_full0 + 8 * stage;
                     if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * stage, PAIR_TX);
-                    tma_load_2d_pair(smem_u32(sA + stage * A_STAGE), &tmA, leader_full, kb * BK, m0);
-                    const uint32_t bdst = smem_u32(sB + stage * B_STAGE);
+                    tma_load_2d_pair(a_dst, &tmA, leader_full, k0, m0);
                     if (B_KMAJOR) {
-                        tma_load_2d_pair(bdst, &tmB, leader_full, kb * BK, n0);
+                        tma_load_2d_pair(b_dst, &tmB, leader_full, k0, n0);
                     } else {
-                        tma_load_2d_pair(bdst, &tmB, leader_full, n0, kb * BK);
-                        tma_load_2d_pair(bdst + BK * 128, &tmB, leader_full, n0 + 64, kb * BK);
+                        tma_load_2d_pair(b_dst, &tmB, leader_full, n0, k0);
+                        tma_load_2d_pair(b_dst + BK * 128, &tmB, leader_full, n0 + 64, k0);
                     }
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    a_dst += A_STAGE; b_dst += B_STAGE;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; a_dst = a_dst0; b_dst = b_dst0; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {  // the pair's single MMA issuer
-            uint32_t stage = 0, phase = 0;
+            constexpr uint32_t DESC_HI = smem_desc_hi_sw128(1024);
+            constexpr uint32_t A_STEP = A_STAGE >> 4, B_STEP = B_STAGE >> 4;
+            constexpr uint32_t A_K16 = 32 >> 4, B_K16 = (B_KMAJOR ? 32 : 2048) >> 4;   // one 16-deep slice further along K
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(sA), 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(sB), B_KMAJOR ? 16 : BK * 128);
+            const uint32_t empty_peer0 = map_to_cta(empty0, 1), tfull_peer0 = map_to_cta(tfull0, 1);
+            uint32_t stage = 0, phase = 0, a_lo = a_lo0, b_lo = b_lo0;
             int it = 0;
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++it) {
@@ -138,26 +150,27 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(full0 + 8 * stage, phase, status, 0x43)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_base = smem_u32(sA + stage * A_STAGE), b_base = smem_u32(sB + stage * B_STAGE);
+                    umma_f16_pair(d_tmem, smem_desc_join(a_lo, DESC_HI), smem_desc_join(b_lo, DESC_HI), IDESC, kb != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k4 = 0; k4 < BK / 16; ++k4) {
-                        const uint64_t adesc = make_smem_desc_sw128(a_base + k4 * 32, 16, 1024);
-                        const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_base + k4 * 32, 16, 1024)
-                                                        : make_smem_desc_sw128(b_base + k4 * 2048, BK * 128, 1024);
-                        umma_f16_pair(d_tmem, adesc, bdesc, IDESC, (kb | k4) != 0 ? 1u : 0u);
-                    }
-                    umma_commit_pair(map_to_cta(empty0 + 8 * stage, 0));   // free the stage in both CTAs
-                    umma_commit_pair(map_to_cta(empty0 + 8 * stage, 1));
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    for (uint32_t k4 = 1; k4 < BK / 16; ++k4)
+                        umma_f16_pair(d_tmem, smem_desc_join(a_lo + k4 * A_K16, DESC_HI), smem_desc_join(b_lo + k4 * B_K16, DESC_HI), IDESC, 1u);
+                    umma_commit_pair(empty0 + 8 * stage);        // free the stage in both CTAs (own barrier: its shared::cta
+                    umma_commit_pair(empty_peer0 + 8 * stage);   // address is also its cluster address)
+                    a_lo += A_STEP; b_lo += B_STEP;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
                 }
                 if (ok) {
-                    umma_commit_pair(map_to_cta(tfull0 + 8 * acc, 0));     // accumulator ready in both CTAs
-                    umma_commit_pair(map_to_cta(tfull0 + 8 * acc, 1));
+                    umma_commit_pair(tfull0 + 8 * acc);          // accumulator ready in both CTAs
+                    umma_commit_pair(tfull_peer0 + 8 * acc);
                 }
             }
         }
     } else {
         const int wq = warp & 3;
+        const uint32_t tempty_leader0 = map_to_cta(tempty0, 0);
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(wq * 32) << 16);
+        const T* addp = reinterpret_cast<const T*>(ep.add);
+        const float scalar_add = ep.add_mode == PYC_B200_ADD_SCALAR ? ep.add_scale * E::to_f(addp[0]) : 0.0f;
         int it = 0;
         for (int tile = pair; tile < num_tiles; tile += pairs, ++it) {
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
@@ -168,56 +181,67 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase, status, 0x44)) break;
             tc_fence_after();
             T* drow = reinterpret_cast<T*>(ep.D) + static_cast<size_t>(row) * N;
-            const T* addp = reinterpret_cast<const T*>(ep.add);
-            float scalar_add = 0.0f;
-            if (ep.add_mode == PYC_B200_ADD_SCALAR) scalar_add = ep.add_scale * E::to_f(addp[0]);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * BN + c * 32, r);
-                tmem_ld_wait();
+            const uint32_t acc_addr = lane_base + acc * BN;
+            // One 32-column chunk: scale, add, activation, 64 bytes out.  The next chunk's TMEM load is already in flight.
+            auto chunk = [&](const uint32_t (&r)[32], int c) {
                 const int col0 = n0 + c * 32;  // warp-uniform
-                if (col0 < N && row < M) {
-                    float v[32];
+                if (col0 >= N || row >= M) return;
+                float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = ep.alpha * __uint_as_float(r[j]) + scalar_add;
-                    const bool full_chunk = ep.vec_ok && (col0 + 32 <= N);
-                    if (ep.add_mode == PYC_B200_ADD_ROW_BIAS || ep.add_mode == PYC_B200_ADD_MATRIX) {
-                        const T* src = ep.add_mode == PYC_B200_ADD_ROW_BIAS ? addp + col0 : addp + static_cast<size_t>(row) * N + col0;
-                        if (full_chunk) {
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const uint4 u = __ldg(reinterpret_cast<const uint4*>(src) + q);
-                                float a, b;
-                                E::unpack(u.x, a, b); v[q * 8 + 0] += ep.add_scale * a; v[q * 8 + 1] += ep.add_scale * b;
-                                E::unpack(u.y, a, b); v[q * 8 + 2] += ep.add_scale * a; v[q * 8 + 3] += ep.add_scale * b;
-                                E::unpack(u.z, a, b); v[q * 8 + 4] += ep.add_scale * a; v[q * 8 + 5] += ep.add_scale * b;
-                                E::unpack(u.w, a, b); v[q * 8 + 6] += ep.add_scale * a; v[q * 8 + 7] += ep.add_scale * b;
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j) if (col0 + j < N) v[j] += ep.add_scale * E::to_f(src[j]);
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = apply_activation(v[j], ep.act);
+                for (int j = 0; j < 32; ++j) v[j] = ep.alpha * __uint_as_float(r[j]) + scalar_add;
+                const bool full_chunk = ep.vec_ok && (col0 + 32 <= N);
+                if (ep.add_mode == PYC_B200_ADD_ROW_BIAS || ep.add_mode == PYC_B200_ADD_MATRIX) {
+                    const T* src = ep.add_mode == PYC_B200_ADD_ROW_BIAS ? addp + col0 : addp + static_cast<size_t>(row) * N + col0;
                     if (full_chunk) {
-                        uint4* dst = reinterpret_cast<uint4*>(drow + col0);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            uint4 u;
-                            u.x = E::pack(v[q * 8 + 0], v[q * 8 + 1]); u.y = E::pack(v[q * 8 + 2], v[q * 8 + 3]);
-                            u.z = E::pack(v[q * 8 + 4], v[q * 8 + 5]); u.w = E::pack(v[q * 8 + 6], v[q * 8 + 7]);
-                            dst[q] = u;
+                            const uint4 u = __ldg(reinterpret_cast<const uint4*>(src) + q);
+                            float a, b;
+                            E::unpack(u.x, a, b); v[q * 8 + 0] += ep.add_scale * a; v[q * 8 + 1] += ep.add_scale * b;
+                            E::unpack(u.y, a, b); v[q * 8 + 2] += ep.add_scale * a; v[q * 8 + 3] += ep.add_scale * b;
+                            E::unpack(u.z, a, b); v[q * 8 + 4] += ep.add_scale * a; v[q * 8 + 5] += ep.add_scale * b;
+                            E::unpack(u.w, a, b); v[q * 8 + 6] += ep.add_scale * a; v[q * 8 + 7] += ep.add_scale * b;
                         }
                     } else {
-                        for (int j = 0; j < 32; ++j) if (col0 + j < N) drow[col0 + j] = E::from_f(v[j]);
+                        for (int j = 0; j < 32; ++j) if (col0 + j < N) v[j] += ep.add_scale * E::to_f(src[j]);
                     }
                 }
+                if (ep.act == PYC_B200_ACT_GELU) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) gelu_erf_x2(v[j], v[j + 1]);
+                } else if (ep.act == PYC_B200_ACT_RELU) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+                }
+                if (full_chunk) {
+                    uint4* dst = reinterpret_cast<uint4*>(drow + col0);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint4 u;
+                        u.x = E::pack(v[q * 8 + 0], v[q * 8 + 1]); u.y = E::pack(v[q * 8 + 2], v[q * 8 + 3]);
+                        u.z = E::pack(v[q * 8 + 4], v[q * 8 + 5]); u.w = E::pack(v[q * 8 + 6], v[q * 8 + 7]);
+                        dst[q] = u;
+                    }
+                } else {
+                    for (int j = 0; j < 32; ++j) if (col0 + j < N) drow[col0 + j] = E::from_f(v[j]);
+                }
+            };
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(acc_addr, r0);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c += 2) {
+                tmem_ld_wait();
+                tmem_ld_32x32(acc_addr + (c + 1) * 32, r1);
+                chunk(r0, c);
+                __syncwarp();
+                tmem_ld_wait();
+                if (c + 2 < BN / 32) tmem_ld_32x32(acc_addr + (c + 2) * 32, r0);
+                chunk(r1, c + 1);
                 __syncwarp();
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty0 + 8 * acc, 0));  // the leader's MMA thread waits for all 8 warps
+            if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * acc);  // the leader's MMA thread waits for all 8 warps
         }
     }
 

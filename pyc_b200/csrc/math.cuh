@@ -31,6 +31,48 @@ __device__ __forceinline__ float gelu_erf(float v) {
     return v < 0.0f ? h : v - h;
 }
 
+// Two fp32 lanes per instruction (fma/mul .f32x2): the polynomial of two elements costs the issue slots of one.
+// Matters where the activation runs beside a tensor-core main loop whose single issuing thread needs those slots.
+__device__ __forceinline__ unsigned long long f32x2_pack(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void f32x2_unpack(unsigned long long v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long f32x2_fma(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long f32x2_mul(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ unsigned long long f32x2_splat(float a) { return f32x2_pack(a, a); }
+
+// gelu_erf on two values at once; same polynomial, same results as the scalar form up to the sign assembly, which is
+// written as max(v, 0) - |0.5 * v * erfc(x)| (equal to the scalar form's two cases).
+__device__ __forceinline__ void gelu_erf_x2(float& v0, float& v1) {
+    const float x0 = fminf(fabsf(v0) * 0.70710678118654752f, 4.2f), x1 = fminf(fabsf(v1) * 0.70710678118654752f, 4.2f);
+    const unsigned long long x = f32x2_pack(x0, x1);
+    unsigned long long q = f32x2_splat(-4.536098769e-05f);      // coefficients negated: the product below is -x * Q(x)
+    q = f32x2_fma(q, x, f32x2_splat(4.455243683e-04f));
+    q = f32x2_fma(q, x, f32x2_splat(-1.489487318e-03f));
+    q = f32x2_fma(q, x, f32x2_splat(-7.745675391e-04f));
+    q = f32x2_fma(q, x, f32x2_splat(2.825363673e-02f));
+    q = f32x2_fma(q, x, f32x2_splat(-1.484815990e-01f));
+    q = f32x2_fma(q, x, f32x2_splat(-9.184163958e-01f));
+    q = f32x2_fma(q, x, f32x2_splat(-1.627908593e+00f));
+    float t0, t1;
+    f32x2_unpack(f32x2_mul(x, q), t0, t1);
+    const float h0 = v0 * ex2_approx(t0), h1 = v1 * ex2_approx(t1);   // v * erfc(x)
+    v0 = fmaf(-0.5f, fabsf(h0), fmaxf(v0, 0.0f));
+    v1 = fmaf(-0.5f, fabsf(h1), fmaxf(v1, 0.0f));
+}
+
 __device__ __forceinline__ float apply_activation(float v, int act) {
     if (act == 1 /* PYC_B200_ACT_RELU */) return v > 0.0f ? v : 0.0f;
     if (act == 2 /* PYC_B200_ACT_GELU */) return gelu_erf(v);

@@ -216,6 +216,20 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
     return d;
 }
 
+// The same descriptor split in two 32-bit words, for issue loops that step through a ring of stages: the high word
+// (stride-byte-offset, version, swizzle mode) never changes, and stepping the operand address by `bytes` is one
+// 32-bit add of bytes >> 4 to the low word (address field bits 0-13, leading-byte-offset bits 16-29; the sum is
+// again a shared-memory address, so it cannot carry out of its field).
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__host__ __device__ constexpr uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint64_t smem_desc_join(uint32_t lo, uint32_t hi) {
+    return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
 // Instruction descriptor for kind::f16 / kind::f8f6f4: fp32 accumulate,
 // a_fmt/b_fmt (f16: 0 = f16, 1 = bf16; f8f6f4: 0 = e4m3, 1 = e5m2),
 // a_mn / b_mn = 1 when that operand is MN-major in shared memory.
