@@ -27,6 +27,7 @@
 #include <string.h>
 
 #include "internal.h"
+#include "math.cuh"
 #include "ptx_sm100.cuh"
 
 namespace b200 {
@@ -47,6 +48,17 @@ template <> struct AElem<0> {
 
 // 2^x on the MUFU in one instruction (flush-to-zero; exp2f() adds range handling the softmax does not need:
 // arguments are <= 0 up to the lazy-rescale margin and -inf gives 0).
+// max of three in one instruction (sm_100 max.f32 with three sources)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long f32x2_add(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -392,13 +404,18 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            // Descriptor high words are constants and the low words differ from a per-stage base by compile-time steps, so
+            // an MMA costs this thread one add besides its own issue: the thread shares its scheduler with softmax warps.
+            constexpr uint32_t HI_K = smem_desc_hi_sw128(1024);
+            const uint32_t q_lo = smem_desc_lo(sQ, 16), k_lo0 = smem_desc_lo(sK, 16), v_lo0 = smem_desc_lo(sV, KV_SLAB);
             auto issue_qk = [&](int j) {  // S[j&1] = Q K_j^T, 128 x 64 x HD
                 const int st = j & 1;
                 const uint32_t d = tmem_base + (j & 1) * BKV2;
+                const uint32_t k_lo = k_lo0 + st * (SM::KV_TILE >> 4);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)
-                    umma_f16(d, make_smem_desc_sw128(sQ + (ks / 4) * Q_SLAB + (ks % 4) * 32, 16, 1024),
-                             make_smem_desc_sw128(sK + st * SM::KV_TILE + (ks / 4) * KV_SLAB + (ks % 4) * 32, 16, 1024), IDESC_QK, ks != 0);
+                    umma_f16(d, smem_desc_join(q_lo + (((ks / 4) * Q_SLAB + (ks % 4) * 32) >> 4), HI_K),
+                             smem_desc_join(k_lo + (((ks / 4) * KV_SLAB + (ks % 4) * 32) >> 4), HI_K), IDESC_QK, ks != 0);
                 umma_commit(s_full + 8 * (j & 1));
                 umma_commit(k_empty + 8 * st);
             };
@@ -414,9 +431,10 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 if (!mbar_wait(p_full + 8 * (j & 1), (j >> 1) & 1, status, 0x56)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t p_tmem = tmem_base + (j & 1) * BKV2;   // P_j sits where S_j was: 32 columns of packed pairs
+                const uint32_t v_lo = v_lo0 + st * (SM::KV_TILE >> 4);
 #pragma unroll
                 for (int ks = 0; ks < BKV2 / 16; ++ks)  // O += P_j V_j : 128 x HD x 64, A from TMEM (8 columns per 16 keys)
-                    umma_f16_ts(tmem_base + O_COL, p_tmem + ks * 8, make_smem_desc_sw128(sV + st * SM::KV_TILE + ks * 2048, KV_SLAB, 1024),
+                    umma_f16_ts(tmem_base + O_COL, p_tmem + ks * 8, smem_desc_join(v_lo + ks * (2048 >> 4), HI_K),
                                 IDESC_PV, (j | ks) != 0 ? 1u : 0u);
                 umma_commit(v_empty + 8 * st);
                 umma_commit(pv_done);
@@ -456,12 +474,12 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                     if (k0 + 32 + t >= k_lim) r1[t] = 0xff800000u;
                 }
             }
-            {   // four independent chains instead of one 64-deep dependency
+            {   // four independent chains instead of one 64-deep dependency; three-input max halves the instruction count
                 float mx[4] = {m_blk, m_blk, m_blk, m_blk};
 #pragma unroll
                 for (int t = 0; t < 32; t += 4) {
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], fmaxf(__uint_as_float(r0[t + u]), __uint_as_float(r1[t + u])));
+                    for (int u = 0; u < 4; ++u) mx[u] = fmax3(mx[u], __uint_as_float(r0[t + u]), __uint_as_float(r1[t + u]));
                 }
                 m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             }
@@ -473,18 +491,27 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             const float m_ref = move ? m_new : m_run;
             const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
             const float alpha = move ? fast_exp2(m_run - m_use) : 1.0f;   // m_run = -inf -> 0
-            float l_part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // exponent arguments and row sums two lanes per instruction (fma/add .f32x2); the exponentials themselves are
+            // one special-function op each
+            const unsigned long long sc2 = f32x2_splat(ap.scale_log2), mu2 = f32x2_splat(-m_use);
+            unsigned long long l2[4] = {0ull, 0ull, 0ull, 0ull};   // bit pattern of (0.0f, 0.0f)
             uint32_t packed[32];
 #pragma unroll
             for (int t = 0; t < 32; t += 2) {
-                // one element in four goes to the FMA-pipe polynomial (compile-time pattern after unrolling)
-                const float a0 = fast_exp2(fmaf(__uint_as_float(r0[t]), ap.scale_log2, -m_use)), a1 = fast_exp2(fmaf(__uint_as_float(r0[t + 1]), ap.scale_log2, -m_use));
-                const float b0 = fast_exp2(fmaf(__uint_as_float(r1[t]), ap.scale_log2, -m_use));
-                const float b1x = fmaf(__uint_as_float(r1[t + 1]), ap.scale_log2, -m_use);
-                const float b1 = POLY ? poly_exp2(b1x) : fast_exp2(b1x);
-                l_part[(t >> 1) & 3] += (a0 + a1) + (b0 + b1);
+                float xa0, xa1, xb0, xb1;
+                f32x2_unpack(f32x2_fma(f32x2_pack(__uint_as_float(r0[t]), __uint_as_float(r0[t + 1])), sc2, mu2), xa0, xa1);
+                f32x2_unpack(f32x2_fma(f32x2_pack(__uint_as_float(r1[t]), __uint_as_float(r1[t + 1])), sc2, mu2), xb0, xb1);
+                const float a0 = fast_exp2(xa0), a1 = fast_exp2(xa1), b0 = fast_exp2(xb0);
+                const float b1 = POLY ? poly_exp2(xb1) : fast_exp2(xb1);   // optionally one element in four on the FMA pipe
+                l2[(t >> 1) & 3] = f32x2_add(l2[(t >> 1) & 3], f32x2_add(f32x2_pack(a0, a1), f32x2_pack(b0, b1)));
                 packed[t / 2] = E::pack(a0, a1);          // keys k0 + t, t+1      -> column t/2
                 packed[16 + t / 2] = E::pack(b0, b1);     // keys k0 + 32 + t, ..  -> column 16 + t/2
+            }
+            float l_part[4];
+            {
+                float lo, hi;
+                f32x2_unpack(f32x2_add(f32x2_add(l2[0], l2[1]), f32x2_add(l2[2], l2[3])), lo, hi);
+                l_part[0] = lo; l_part[1] = hi; l_part[2] = 0.0f; l_part[3] = 0.0f;
             }
             l_run = l_run * alpha + ((l_part[0] + l_part[1]) + (l_part[2] + l_part[3]));
             m_run = m_ref;
