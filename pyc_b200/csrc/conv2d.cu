@@ -103,25 +103,32 @@ conv2d_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+            const uint32_t a_dst0 = smem_u32(sA), b_dst0 = smem_u32(sB);
+            uint32_t stage = 0, phase = 0, adst = a_dst0, bdst = b_dst0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 int kt, n0, p0, q0;
                 tile_origin(tile, kt, n0, p0, q0);
+                // k-block kb = (r * S + s) * c_chunks + cc, walked with counters instead of divisions
+                int cc = 0, s = 0, r = 0, rs = 0;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    const int cc = kb % c_chunks, rs = kb / c_chunks, s = rs % cp.S, r = rs / cp.S;
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, status, 0x11)) { ok = false; break; }
                     const uint32_t fb = full0 + 8 * stage;
                     mbar_arrive_expect_tx(fb, STAGE_TX);
-                    tma_load_4d(smem_u32(sA + stage * A_STAGE_BYTES), &tmIn, fb, cc * BK, q0 - cp.pad_w + s, p0 - cp.pad_h + r, n0);
-                    tma_load_3d(smem_u32(sB + stage * B_STAGE_BYTES), &tmW, fb, cc * BK, rs, kt * BN);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    tma_load_4d(adst, &tmIn, fb, cc * BK, q0 - cp.pad_w + s, p0 - cp.pad_h + r, n0);
+                    tma_load_3d(bdst, &tmW, fb, cc * BK, rs, kt * BN);
+                    if (++cc == c_chunks) { cc = 0; ++rs; if (++s == cp.S) { s = 0; ++r; } }
+                    adst += A_STAGE_BYTES; bdst += B_STAGE_BYTES;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; adst = a_dst0; bdst = b_dst0; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+            // constant descriptor high word, stepped low words (this thread shares its scheduler with an epilogue warp)
+            constexpr uint32_t DESC_HI = smem_desc_hi_sw128(1024);
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(sA), 16), b_lo0 = smem_desc_lo(smem_u32(sB), 16);
+            uint32_t stage = 0, phase = 0, a_lo = a_lo0, b_lo = b_lo0;
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
@@ -132,13 +139,13 @@ conv2d_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(full0 + 8 * stage, phase, status, 0x13)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES), b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+                    umma_f16(d_tmem, smem_desc_join(a_lo, DESC_HI), smem_desc_join(b_lo, DESC_HI), IDESC, kb != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k4 = 0; k4 < BK / 16; ++k4)
-                        umma_f16(d_tmem, make_smem_desc_sw128(a_base + k4 * 32, 16, 1024), make_smem_desc_sw128(b_base + k4 * 32, 16, 1024),
-                                 IDESC, (kb | k4) != 0 ? 1u : 0u);
+                    for (uint32_t k4 = 1; k4 < BK / 16; ++k4)
+                        umma_f16(d_tmem, smem_desc_join(a_lo + k4 * 2, DESC_HI), smem_desc_join(b_lo + k4 * 2, DESC_HI), IDESC, 1u);
                     umma_commit(empty0 + 8 * stage);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    a_lo += A_STAGE_BYTES >> 4; b_lo += B_STAGE_BYTES >> 4;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
                 }
                 if (ok) umma_commit(tfull0 + 8 * acc);
             }

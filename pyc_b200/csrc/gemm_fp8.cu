@@ -81,7 +81,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+            const uint32_t a_dst0 = smem_u32(sA), b_dst0 = smem_u32(sB);
+            uint32_t stage = 0, phase = 0, adst = a_dst0, bdst = b_dst0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 int tm, tn;
@@ -91,21 +92,28 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, status, 0x31)) { ok = false; break; }
                     const uint32_t fb = full0 + 8 * stage;
                     mbar_arrive_expect_tx(fb, STAGE_TX);
-                    tma_load_2d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, fb, kb * BK, m0);
-                    const uint32_t bdst = smem_u32(sB + stage * B_STAGE_BYTES);
+                    tma_load_2d(adst, &tmA, fb, kb * BK, m0);
                     if (B_KMAJOR) {
                         tma_load_2d(bdst, &tmB, fb, kb * BK, n0);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 128; ++j) tma_load_2d(bdst + j * (BK * 128), &tmB, fb, n0 + j * 128, kb * BK);
                     }
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    adst += A_STAGE_BYTES; bdst += B_STAGE_BYTES;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; adst = a_dst0; bdst = b_dst0; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+            // Constant descriptor high word, stepped low words: the loop must come round once per k-block of tensor time
+            // while an epilogue warp competes for the same scheduler.
+            constexpr uint32_t DESC_HI = smem_desc_hi_sw128(1024);
+            constexpr uint32_t A_STEP = A_STAGE_BYTES >> 4, B_STEP = B_STAGE_BYTES >> 4;
+            constexpr uint32_t A_K32 = 32 >> 4, B_K32 = (B_KMAJOR ? 32 : 32 * 128) >> 4;   // 32 k-values further along K
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(sA), 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(sB), B_KMAJOR ? 16 : BK * 128);
+            uint32_t stage = 0, phase = 0, a_lo = a_lo0, b_lo = b_lo0;
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
@@ -116,16 +124,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(full0 + 8 * stage, phase, status, 0x33)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES), b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+                    umma_f8(d_tmem, smem_desc_join(a_lo, DESC_HI), smem_desc_join(b_lo, DESC_HI), IDESC, kb != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k4 = 0; k4 < BK / 32; ++k4) {  // one MMA = 32 k-values = 32 bytes of a K-major row
-                        const uint64_t adesc = make_smem_desc_sw128(a_base + k4 * 32, 16, 1024);
-                        const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_base + k4 * 32, 16, 1024)
-                                                        : make_smem_desc_sw128(b_base + k4 * (32 * 128), BK * 128, 1024);
-                        umma_f8(d_tmem, adesc, bdesc, IDESC, (kb | k4) != 0 ? 1u : 0u);
-                    }
+                    for (uint32_t k4 = 1; k4 < BK / 32; ++k4)  // one MMA = 32 k-values = 32 bytes of a K-major row
+                        umma_f8(d_tmem, smem_desc_join(a_lo + k4 * A_K32, DESC_HI), smem_desc_join(b_lo + k4 * B_K32, DESC_HI), IDESC, 1u);
                     umma_commit(empty0 + 8 * stage);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    a_lo += A_STEP; b_lo += B_STEP;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
                 }
                 if (ok) umma_commit(tfull0 + 8 * acc);
             }
@@ -145,13 +150,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tc_fence_after();
             const float rs = (ep.row_scale && row < M) ? ep.row_scale[row] : 1.0f;
             __nv_bfloat16* drow = ep.D + static_cast<size_t>(row) * N;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * BN + c * 32, r);
-                tmem_ld_wait();
+            const uint32_t acc_addr = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * BN;
+            // One 32-column chunk; the next chunk's TMEM load is already in flight while this one is computed.
+            auto chunk = [&](const uint32_t (&r)[32], int c) {
                 const int col0 = n0 + c * 32;  // warp-uniform
-                if (col0 < N && row < M) {
+                if (col0 >= N || row >= M) return;
+                {
                     float v[32];
                     const bool full_chunk = vec_ok && col0 + 32 <= N;
                     if (full_chunk) {  // scales and bias as 16-byte loads: every lane reads the same 128 / 64 bytes (broadcast)
@@ -173,8 +177,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                 for (int t = 0; t < 4; ++t) { v[q * 8 + 2 * t] += __uint_as_float(w[t] << 16); v[q * 8 + 2 * t + 1] += __uint_as_float(w[t] & 0xffff0000u); }
                             }
                         }
+                        if (ep.act == PYC_B200_ACT_GELU) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = apply_activation(v[j], ep.act);
+                            for (int j = 0; j < 32; j += 2) gelu_erf_x2(v[j], v[j + 1]);
+                        } else if (ep.act == PYC_B200_ACT_RELU) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+                        }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
@@ -202,6 +211,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         for (int j = 0; j < 32; ++j) if (col0 + j < N) drow[col0 + j] = __float2bfloat16_rn(v[j]);
                     }
                 }
+            };
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(acc_addr, r0);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c += 2) {
+                tmem_ld_wait();
+                tmem_ld_32x32(acc_addr + (c + 1) * 32, r1);
+                chunk(r0, c);
+                __syncwarp();
+                tmem_ld_wait();
+                if (c + 2 < BN / 32) tmem_ld_32x32(acc_addr + (c + 2) * 32, r0);
+                chunk(r1, c + 1);
                 __syncwarp();
             }
             tc_fence_before();
