@@ -256,15 +256,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
                 }
                 if (full_chunk) {
-                    uint4* dst = reinterpret_cast<uint4*>(drow + col0);
+                    // 64 bytes of this row: two 32-byte stores when the row start allows it (whole sectors), else four 16-byte ones
+                    uint32_t w[16];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        uint4 u;
-                        u.x = E::pack(v[q * 8 + 0], v[q * 8 + 1]);
-                        u.y = E::pack(v[q * 8 + 2], v[q * 8 + 3]);
-                        u.z = E::pack(v[q * 8 + 4], v[q * 8 + 5]);
-                        u.w = E::pack(v[q * 8 + 6], v[q * 8 + 7]);
-                        dst[q] = u;
+                    for (int j = 0; j < 16; ++j) w[j] = E::pack(v[2 * j], v[2 * j + 1]);
+                    if (ep.vec_ok == 2) {
+                        const uint32_t lo[8] = {w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]};
+                        const uint32_t hi[8] = {w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]};
+                        st_global_v8(drow + col0, lo);
+                        st_global_v8(drow + col0 + 16, hi);
+                    } else {
+                        uint4* dst = reinterpret_cast<uint4*>(drow + col0);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
                     }
                 } else {
                     for (int j = 0; j < 32; ++j)
@@ -341,7 +345,7 @@ int launch_instance(const GemmProblem& p, cudaStream_t stream, int* status) {
     const bool aligned = (reinterpret_cast<uintptr_t>(p.D) % 16 == 0) && (p.N % 8 == 0) &&
                          (ep.add_mode == PYC_B200_ADD_NONE || ep.add_mode == PYC_B200_ADD_SCALAR ||
                           reinterpret_cast<uintptr_t>(p.add) % 16 == 0);
-    ep.vec_ok = aligned ? 1 : 0;
+    ep.vec_ok = aligned ? ((reinterpret_cast<uintptr_t>(p.D) % 32 == 0 && p.N % 16 == 0) ? 2 : 1) : 0;   // 2: rows start on 32-byte boundaries
     tile_order_from_env(&ep.group_m, &ep.l2_hints);
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
@@ -425,6 +429,7 @@ int launch_static_instance(const GemmProblem& p, cudaStream_t stream, StaticDevi
     ep.add_mode = p.add ? p.add_mode : PYC_B200_ADD_NONE; ep.act = p.act;
     ep.vec_ok = ((reinterpret_cast<uintptr_t>(p.D) % 16 == 0) && (p.N % 8 == 0) &&
                  (ep.add_mode == PYC_B200_ADD_NONE || ep.add_mode == PYC_B200_ADD_SCALAR || reinterpret_cast<uintptr_t>(p.add) % 16 == 0)) ? 1 : 0;
+    if (ep.vec_ok && reinterpret_cast<uintptr_t>(p.D) % 32 == 0 && p.N % 16 == 0) ep.vec_ok = 2;   // rows start on 32-byte boundaries
     tile_order_from_env(&ep.group_m, &ep.l2_hints);
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     // The block keeps whatever the previous call left: the status word must start at zero.

@@ -64,6 +64,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     return false;
 }
 
+// 32-byte global store (one full sector per thread); `p` must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+
 // --------------------------------------------------------------------- TMA --
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
