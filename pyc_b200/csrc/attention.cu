@@ -21,6 +21,7 @@
 //
 // Layout: Q, K, V, Out are [batch_heads, seq, d] contiguous; tensor maps are 3-D
 // (d, seq, batch_heads) so rows past `seq` read as zeros instead of the next head.
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdlib.h>
@@ -536,6 +537,10 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + 8 * (j & 1));
         }
+        // The last P*V.  A parity wait is only meaningful when at most one completion is outstanding, and a warp may be a
+        // whole key block ahead of the slowest one (whose P gates the previous P*V): wait for the previous P*V first.
+        // Its own validity: Q*K^T of the last block was issued behind P*V of block nblk-3, so nblk-2 completions are certain.
+        if (ok && nblk >= 2) ok = mbar_wait(pv_done, (nblk - 2) & 1, status, 0x5b);
         if (ok && mbar_wait(pv_done, (nblk - 1) & 1, status, 0x5a)) {
             tc_fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
@@ -558,6 +563,345 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                     }
                 }
                 __syncwarp();
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*reinterpret_cast<volatile int*>(status) != ST_OK) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Third kernel: the second kernel made persistent.  A CTA that handles one query block pays
+// for its launch, barrier and TMEM set-up, the Q load before the first score block and the
+// teardown; at 2048 keys that fixed part is a sizeable share of a causal CTA's life.  Here the
+// grid is two CTAs per SM and every CTA keeps drawing work units from a global counter:
+// barriers, TMEM and the K/V ring live across query blocks, the next Q is loaded as soon as
+// the last Q*K^T of the current block has been issued, and the next block's first two score
+// blocks are issued right behind the last P*V.  All pipeline counters (K/V stage, S buffer,
+// P*V phase) run on ONE global key-block counter per role, so nothing is re-initialised
+// between query blocks.  The producer thread draws the unit (atomicAdd) and hands it to the
+// MMA thread and the softmax warps through a two-slot ring in shared memory.
+// Work units: non-causal, one query block; causal, the pair (last - i, i) of one head, so
+// that units are of equal length and the last units drawn are not the longest.  Units of one
+// head are neighbours in the counter's order, so its K/V stay in L2.
+// ---------------------------------------------------------------------------------------
+template <int HD>
+struct AttnSmem3 {
+    static constexpr int Q_BYTES = BQ * HD * 2;
+    static constexpr int KV_TILE = BKV2 * HD * 2;
+    static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = Q_BYTES + 2 * KV_TILE, BAR_OFF = Q_BYTES + 4 * KV_TILE;
+    static constexpr int NUM_BARS = 20;
+    static constexpr size_t BYTES = 1024 + BAR_OFF + NUM_BARS * 8 + 32;   // + TMEM slot + two schedule slots
+};
+
+struct AttnWork {   // unit number -> query blocks
+    int num_qb, units_per_head, total_units;
+    __device__ __forceinline__ int blocks_in_unit(int unit, bool causal) const {
+        if (!causal) return 1;
+        const int i = unit % units_per_head;
+        return (num_qb - 1 - i) != i ? 2 : 1;
+    }
+    // q-block `part` (0 or 1) of `unit`: the long one first
+    __device__ __forceinline__ void item(int unit, int part, bool causal, int& qb, int& bh) const {
+        bh = unit / units_per_head;
+        const int i = unit % units_per_head;
+        if (!causal) { qb = num_qb - 1 - i; return; }
+        qb = part == 0 ? num_qb - 1 - i : i;
+    }
+};
+
+template <int HD, int FMT, bool POLY>
+__global__ void __launch_bounds__(192, 2)
+attention_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, AttnParams ap, int* status, int* next_unit) {
+    using SM = AttnSmem3<HD>;
+    using E = AElem<FMT>;
+    using T = typename E::T;
+    constexpr int HALVES = HD / 64;
+    constexpr int Q_SLAB = BQ * 128;
+    constexpr int KV_SLAB = BKV2 * 128;
+    constexpr uint32_t IDESC_QK = make_idesc(FMT, FMT, 0, 0, BQ, BKV2);
+    constexpr uint32_t IDESC_PV = make_idesc(FMT, FMT, 0, 1, BQ, HD);
+    constexpr uint32_t TMEM_COLS = 256;              // S0 @0, S1 @64, O @128
+    constexpr uint32_t O_COL = 128;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + SM::NUM_BARS);
+    volatile int* sched = reinterpret_cast<volatile int*>(tmem_slot + 1);   // two slots: the unit each role works on next
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 24, v_full = bar0 + 40, v_empty = bar0 + 56,
+                   s_full = bar0 + 72, p_full = bar0 + 88, pv_done = bar0 + 104, q_empty = bar0 + 112, o_free = bar0 + 120,
+                   sched_full = bar0 + 128, sched_empty = bar0 + 144;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool causal = ap.causal != 0;
+    AttnWork wk;
+    wk.num_qb = (ap.seq + BQ - 1) / BQ;
+    wk.units_per_head = causal ? (wk.num_qb + 1) / 2 : wk.num_qb;
+    wk.total_units = wk.units_per_head * ap.batch_heads;
+    const int kv_blocks_all = (ap.seq + BKV2 - 1) / BKV2;
+    auto blocks_of = [&](int qb) { return causal ? min(kv_blocks_all, (qb * BQ + BQ + BKV2 - 1) / BKV2) : kv_blocks_all; };
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+        mbar_init(q_full, 1); mbar_init(q_empty, 1); mbar_init(o_free, 4);
+        for (int i = 0; i < 2; ++i) { mbar_init(sched_full + 8 * i, 1); mbar_init(sched_empty + 8 * i, 5); }   // readers: MMA thread + 4 warps
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full + 8 * i, 1); mbar_init(k_empty + 8 * i, 1);
+            mbar_init(v_full + 8 * i, 1); mbar_init(v_empty + 8 * i, 1);
+            mbar_init(s_full + 8 * i, 1); mbar_init(p_full + 8 * i, 4);
+        }
+        mbar_init(pv_done, 1);
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    const uint32_t sQ = smem_u32(smem + SM::Q_OFF), sK = smem_u32(smem + SM::K_OFF), sV = smem_u32(smem + SM::V_OFF);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t g = 0;      // key blocks loaded so far (all query blocks of this CTA)
+            int item = 0;        // query blocks started so far
+            bool ok = true;
+            // Units are handed out by a global counter (SMs do not all run at the same speed, so a static split leaves the
+            // slow ones behind); this thread draws the next unit and publishes it to the other roles through a two-slot ring.
+            // The draw for the unit after this one is issued before this unit's loads and only looked at after them, so the
+            // counter's round trip to L2 is not on the path of the next Q load.
+            int unit = atomicAdd(next_unit, 1);
+            for (uint32_t n = 0; ok; ++n) {
+                const uint32_t slot = n & 1;
+                if (!mbar_wait(sched_empty + 8 * slot, ((n >> 1) & 1) ^ 1, status, 0x60)) { ok = false; break; }
+                if (unit >= wk.total_units) unit = -1;
+                sched[slot] = unit;
+                mbar_arrive(sched_full + 8 * slot);
+                if (unit < 0) break;
+                const int this_unit = unit;
+                unit = atomicAdd(next_unit, 1);
+                const int parts = wk.blocks_in_unit(this_unit, causal);
+                for (int part = 0; part < parts && ok; ++part, ++item) {
+                    int qb, bh;
+                    wk.item(this_unit, part, causal, qb, bh);
+                    const int nblk = blocks_of(qb);
+                    if (item > 0 && !mbar_wait(q_empty, (item - 1) & 1, status, 0x61)) { ok = false; break; }
+                    mbar_arrive_expect_tx(q_full, SM::Q_BYTES);
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h) tma_load_3d(sQ + h * Q_SLAB, &tmQ, q_full, h * 64, qb * BQ, bh);
+                    for (int j = 0; j < nblk; ++j, ++g) {
+                        const uint32_t st = g & 1, par = ((g >> 1) & 1) ^ 1;
+                        if (!mbar_wait(k_empty + 8 * st, par, status, 0x62)) { ok = false; break; }
+                        mbar_arrive_expect_tx(k_full + 8 * st, SM::KV_TILE);
+#pragma unroll
+                        for (int h = 0; h < HALVES; ++h) tma_load_3d(sK + st * SM::KV_TILE + h * KV_SLAB, &tmK, k_full + 8 * st, h * 64, j * BKV2, bh);
+                        if (!mbar_wait(v_empty + 8 * st, par, status, 0x63)) { ok = false; break; }
+                        mbar_arrive_expect_tx(v_full + 8 * st, SM::KV_TILE);
+#pragma unroll
+                        for (int h = 0; h < HALVES; ++h) tma_load_3d(sV + st * SM::KV_TILE + h * KV_SLAB, &tmV, v_full + 8 * st, h * 64, j * BKV2, bh);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t HI_K = smem_desc_hi_sw128(1024);
+            const uint32_t q_lo = smem_desc_lo(sQ, 16), k_lo0 = smem_desc_lo(sK, 16), v_lo0 = smem_desc_lo(sV, KV_SLAB);
+            auto issue_qk = [&](uint32_t gq) {  // S[gq&1] = Q K^T for global key block gq
+                const uint32_t st = gq & 1;
+                const uint32_t d = tmem_base + st * BKV2;
+                const uint32_t k_lo = k_lo0 + st * (SM::KV_TILE >> 4);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)
+                    umma_f16(d, smem_desc_join(q_lo + (((ks / 4) * Q_SLAB + (ks % 4) * 32) >> 4), HI_K),
+                             smem_desc_join(k_lo + (((ks / 4) * KV_SLAB + (ks % 4) * 32) >> 4), HI_K), IDESC_QK, ks != 0);
+                umma_commit(s_full + 8 * st);
+                umma_commit(k_empty + 8 * st);
+            };
+            uint32_t g = 0;      // key blocks whose P*V has been issued
+            int item = 0;
+            bool ok = true;
+            for (uint32_t n = 0; ok; ++n) {
+                const uint32_t slot = n & 1;
+                if (!mbar_wait(sched_full + 8 * slot, (n >> 1) & 1, status, 0x6e)) { ok = false; break; }
+                const int unit = sched[slot];
+                mbar_arrive(sched_empty + 8 * slot);
+                if (unit < 0) break;
+                const int parts = wk.blocks_in_unit(unit, causal);
+                for (int part = 0; part < parts && ok; ++part, ++item) {
+                    int qb, bh;
+                    wk.item(unit, part, causal, qb, bh);
+                    const int nblk = blocks_of(qb);
+                    if (!mbar_wait(q_full, item & 1, status, 0x64)) { ok = false; break; }
+                    for (int j = 0; j < 2 && j < nblk && ok; ++j) {   // two score blocks in flight before the first P arrives
+                        if (!mbar_wait(k_full + 8 * ((g + j) & 1), ((g + j) >> 1) & 1, status, 0x65)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_qk(g + j);
+                        if (j == nblk - 1) umma_commit(q_empty);   // Q may be replaced once these MMAs have read it
+                    }
+                    for (int j = 0; j < nblk && ok; ++j, ++g) {
+                        const uint32_t st = g & 1, ph = (g >> 1) & 1;
+                        if (!mbar_wait(v_full + 8 * st, ph, status, 0x66)) { ok = false; break; }
+                        if (!mbar_wait(p_full + 8 * st, ph, status, 0x67)) { ok = false; break; }
+                        // the first P*V of a query block overwrites O: the previous block's rows must have been read out
+                        if (j == 0 && item > 0 && !mbar_wait(o_free, (item - 1) & 1, status, 0x68)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t p_tmem = tmem_base + st * BKV2;
+                        const uint32_t v_lo = v_lo0 + st * (SM::KV_TILE >> 4);
+#pragma unroll
+                        for (int ks = 0; ks < BKV2 / 16; ++ks)
+                            umma_f16_ts(tmem_base + O_COL, p_tmem + ks * 8, smem_desc_join(v_lo + ks * (2048 >> 4), HI_K),
+                                        IDESC_PV, (j | ks) != 0 ? 1u : 0u);
+                        umma_commit(v_empty + 8 * st);
+                        umma_commit(pv_done);
+                        if (j + 2 < nblk) {
+                            if (!mbar_wait(k_full + 8 * st, ((g + 2) >> 1) & 1, status, 0x69)) { ok = false; break; }
+                            tc_fence_after();
+                            issue_qk(g + 2);
+                            if (j + 2 == nblk - 1) umma_commit(q_empty);
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        const int wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(wq * 32) << 16);
+        uint32_t g = 0;          // key blocks whose softmax this warp has done
+        bool ok = true;
+        for (uint32_t n = 0; ok; ++n) {
+            const uint32_t slot = n & 1;
+            if (!mbar_wait(sched_full + 8 * slot, (n >> 1) & 1, status, 0x6f)) { ok = false; break; }
+            const int unit = sched[slot];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sched_empty + 8 * slot);
+            if (unit < 0) break;
+            const int parts = wk.blocks_in_unit(unit, causal);
+            for (int part = 0; part < parts && ok; ++part) {
+                int qb, bh;
+                wk.item(unit, part, causal, qb, bh);
+                const int nblk = blocks_of(qb);
+                const int q0 = qb * BQ;
+                const int qi = q0 + row;
+                float m_run = -INFINITY, l_run = 0.0f;
+                int k_lim = ap.seq;
+                if (causal) k_lim = min(k_lim, qi + 1);
+                for (int j = 0; j < nblk && ok; ++j, ++g) {
+                    const uint32_t st = g & 1, ph = (g >> 1) & 1;
+                    const uint32_t s_addr = lane_addr + st * BKV2;
+                    if (!mbar_wait(s_full + 8 * st, ph, status, 0x6a)) { ok = false; break; }
+                    tc_fence_after();
+                    const int k0 = j * BKV2;
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32x32(s_addr, r0);
+                    tmem_ld_32x32(s_addr + 32, r1);
+                    tmem_ld_wait();
+                    const bool masked = (k0 + BKV2 > ap.seq) || (causal && k0 + BKV2 > q0 + wq * 32 + 1);
+                    float m_blk = -INFINITY;
+                    if (masked) {
+#pragma unroll
+                        for (int t = 0; t < 32; ++t) {
+                            if (k0 + t >= k_lim) r0[t] = 0xff800000u;       // -inf
+                            if (k0 + 32 + t >= k_lim) r1[t] = 0xff800000u;
+                        }
+                    }
+                    {
+                        float mx[4] = {m_blk, m_blk, m_blk, m_blk};
+#pragma unroll
+                        for (int t = 0; t < 32; t += 4) {
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) mx[u] = fmax3(mx[u], __uint_as_float(r0[t + u]), __uint_as_float(r1[t + u]));
+                        }
+                        m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                    }
+                    m_blk *= ap.scale_log2;
+                    // lazy rescale, as in the second kernel: the reference maximum moves only on a jump of more than 2^8
+                    const float m_new = fmaxf(m_run, m_blk);
+                    const bool move = m_new > m_run + 8.0f || m_run == -INFINITY;
+                    const float m_ref = move ? m_new : m_run;
+                    const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+                    const float alpha = move ? fast_exp2(m_run - m_use) : 1.0f;
+                    const unsigned long long sc2 = f32x2_splat(ap.scale_log2), mu2 = f32x2_splat(-m_use);
+                    unsigned long long l2[4] = {0ull, 0ull, 0ull, 0ull};
+                    uint32_t packed[32];
+#pragma unroll
+                    for (int t = 0; t < 32; t += 2) {
+                        float xa0, xa1, xb0, xb1;
+                        f32x2_unpack(f32x2_fma(f32x2_pack(__uint_as_float(r0[t]), __uint_as_float(r0[t + 1])), sc2, mu2), xa0, xa1);
+                        f32x2_unpack(f32x2_fma(f32x2_pack(__uint_as_float(r1[t]), __uint_as_float(r1[t + 1])), sc2, mu2), xb0, xb1);
+                        const float a0 = fast_exp2(xa0), a1 = fast_exp2(xa1), b0 = fast_exp2(xb0);
+                        const float b1 = POLY ? poly_exp2(xb1) : fast_exp2(xb1);
+                        l2[(t >> 1) & 3] = f32x2_add(l2[(t >> 1) & 3], f32x2_add(f32x2_pack(a0, a1), f32x2_pack(b0, b1)));
+                        packed[t / 2] = E::pack(a0, a1);
+                        packed[16 + t / 2] = E::pack(b0, b1);
+                    }
+                    float l_lo, l_hi;
+                    f32x2_unpack(f32x2_add(f32x2_add(l2[0], l2[1]), f32x2_add(l2[2], l2[3])), l_lo, l_hi);
+                    l_run = l_run * alpha + (l_lo + l_hi);
+                    m_run = m_ref;
+                    if (j > 0 && __any_sync(0xffffffffu, move)) {
+                        // P*V of key block g-1 done: it is the (g-1)-th completion of pv_done.  Q*K^T of block g was issued
+                        // behind P*V of g-2, so at least g-1 completions have happened and the parity test cannot alias.
+                        if (!mbar_wait(pv_done, (g - 1) & 1, status, 0x6b)) { ok = false; break; }
+                        tc_fence_after();
+#pragma unroll 1
+                        for (int c = 0; c < HD / 32; ++c) {
+                            uint32_t o[32];
+                            tmem_ld_32x32(lane_addr + O_COL + c * 32, o);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int t = 0; t < 32; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * alpha);
+                            tmem_st_32x32(lane_addr + O_COL + c * 32, o);
+                        }
+                    }
+                    tmem_st_32x32(s_addr, packed);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(p_full + 8 * st);
+                }
+                if (!ok) break;
+                // Rows of this query block out; then O may be overwritten by the next block's first P*V.  A parity wait is only
+                // meaningful when at most one completion is outstanding, and a warp may be a whole key block ahead of the slowest
+                // one (whose P gates the previous P*V): wait for the previous P*V first (g-2 completions are certain here, since
+                // Q*K^T of the last block was issued behind the P*V two blocks earlier), then for the last one.
+                if (g >= 2 && !mbar_wait(pv_done, (g - 2) & 1, status, 0x6d)) { ok = false; break; }
+                if (!mbar_wait(pv_done, (g - 1) & 1, status, 0x6c)) { ok = false; break; }
+                tc_fence_after();
+                const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+                T* orow = reinterpret_cast<T*>(ap.out) + (static_cast<size_t>(bh) * ap.seq + qi) * HD;
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(lane_addr + O_COL + c * 32, r);
+                    tmem_ld_wait();
+                    if (qi < ap.seq) {
+                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 u;
+                            u.x = E::pack(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv);
+                            u.y = E::pack(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv);
+                            u.z = E::pack(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv);
+                            u.w = E::pack(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv);
+                            dst[q4] = u;
+                        }
+                    }
+                    __syncwarp();
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(o_free);
             }
         }
     }
@@ -630,10 +974,15 @@ int launch_rowwarp(const void* q, const void* k, const void* v, void* o, int bh,
 template <int HD, int FMT>
 int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void* k, const void* v, void* out, float scale, int causal,
                         cudaStream_t stream, int* status) {
-    // PYC_B200_ATTENTION_KERNEL=1 selects the first kernel (128-key blocks, P through shared memory, one CTA per SM);
-    // the default is the second one (64-key blocks, P in TMEM, two CTAs per SM).
+    // PYC_B200_ATTENTION_KERNEL=1 selects the first kernel (128-key blocks, P through shared memory, one CTA per SM),
+    // =2 the second (64-key blocks, P in TMEM, two CTAs per SM, one CTA per query block); the default is the third,
+    // the second made persistent.
     const char* pick = getenv("PYC_B200_ATTENTION_KERNEL");
     const bool first = pick && pick[0] == '1';
+    // Without a choice from the environment: causal work (query blocks of very different length, many short ones) goes to the
+    // persistent kernel; non-causal work, where every CTA runs the same long loop, is a few per cent faster with one CTA per
+    // query block (measured at 2048 and 8192 keys).
+    const bool second = pick ? pick[0] == '2' : !causal;
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
     CUtensorMap tq, tk, tv;
@@ -656,6 +1005,28 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
             attr_set[dev] = true;
         }
         kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, ap, status);
+    } else if (!second) {
+        const char* pe = getenv("PYC_B200_ATTENTION_POLY");
+        const bool poly = pe && pe[0] == '1';
+        constexpr size_t smem = AttnSmem3<HD>::BYTES > 76 * 1024 ? AttnSmem3<HD>::BYTES : 76 * 1024;   // two CTAs per SM, 256 TMEM columns each
+        static bool attr_set3[16][2] = {};
+        auto k_poly = attention_tc3_kernel<HD, FMT, true>;
+        auto k_mufu = attention_tc3_kernel<HD, FMT, false>;
+        if (dev < 16 && !attr_set3[dev][poly]) {
+            B200_CUDA_OK(cudaFuncSetAttribute(poly ? k_poly : k_mufu, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            attr_set3[dev][poly] = true;
+        }
+        const int num_qb = (seq + BQ - 1) / BQ;
+        const long long units = static_cast<long long>(causal ? (num_qb + 1) / 2 : num_qb) * bh;
+        const long long slots = 2ll * sm_count();
+        const unsigned ctas = static_cast<unsigned>(units < slots ? units : slots);
+        // work counter of this launch: one of 48 ints behind the status word (launches that overlap in time on different
+        // streams get different ones), zeroed on the launching stream
+        static std::atomic<unsigned> launch_seq{0};
+        int* next_unit = status + 8 + (launch_seq.fetch_add(1) % 48u);
+        B200_CUDA_OK(cudaMemsetAsync(next_unit, 0, sizeof(int), stream));
+        if (poly) k_poly<<<ctas, 192, smem, stream>>>(tq, tk, tv, ap, status, next_unit);
+        else k_mufu<<<ctas, 192, smem, stream>>>(tq, tk, tv, ap, status, next_unit);
     } else {
         // PYC_B200_ATTENTION_POLY=1 moves a quarter of the exp2 work to the FMA pipe (measured slightly slower on B200: the
         // softmax warps are bound by their dependency chains, not by the MUFU; kept as a switch).

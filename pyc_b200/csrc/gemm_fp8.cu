@@ -13,6 +13,7 @@
 // operand with 128-column slabs (LBO = 16 KB, SBO = 1 KB).
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
+#include <stdlib.h>
 
 #include "internal.h"
 #include "math.cuh"
@@ -42,6 +43,88 @@ __device__ __forceinline__ void fp8_tile_coords(int tile, int tiles_m, int tiles
     const int local = tile - g * group;
     tm = first + local % gm;
     tn = local / gm;
+}
+
+// Epilogue of one accumulator tile for one thread (= one row): BN columns from TMEM at `acc_addr`, dequantise, bias,
+// activation, bf16 out.  Shared by the single-CTA and the CTA-pair kernel.
+template <int BN>
+__device__ __forceinline__ void fp8_epilogue_tile(const Fp8Epilogue& ep, uint32_t acc_addr, int row, int n0, int M, int N, bool vec_ok) {
+    const float rs = (ep.row_scale && row < M) ? ep.row_scale[row] : 1.0f;
+    __nv_bfloat16* drow = ep.D + static_cast<size_t>(row) * N;
+    // One 32-column chunk; the next chunk's TMEM load is already in flight while this one is computed.
+    auto chunk = [&](const uint32_t (&r)[32], int c) {
+        const int col0 = n0 + c * 32;  // warp-uniform
+        if (col0 >= N || row >= M) return;
+        {
+            float v[32];
+            const bool full_chunk = vec_ok && col0 + 32 <= N;
+            if (full_chunk) {  // scales and bias as 16-byte loads: every lane reads the same 128 / 64 bytes (broadcast)
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * rs;
+                if (ep.col_scale) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const float4 c4 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + col0) + q);
+                        v[q * 4 + 0] *= c4.x; v[q * 4 + 1] *= c4.y; v[q * 4 + 2] *= c4.z; v[q * 4 + 3] *= c4.w;
+                    }
+                }
+                if (ep.bias) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint4 u = __ldg(reinterpret_cast<const uint4*>(ep.bias + col0) + q);
+                        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) { v[q * 8 + 2 * t] += __uint_as_float(w[t] << 16); v[q * 8 + 2 * t + 1] += __uint_as_float(w[t] & 0xffff0000u); }
+                    }
+                }
+                if (ep.act == PYC_B200_ACT_GELU) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) gelu_erf_x2(v[j], v[j + 1]);
+                } else if (ep.act == PYC_B200_ACT_RELU) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int col = col0 + j;
+                    float x = __uint_as_float(r[j]) * rs;
+                    if (col < N) {
+                        if (ep.col_scale) x *= __ldg(ep.col_scale + col);
+                        if (ep.bias) x += __bfloat162float(ep.bias[col]);
+                    }
+                    v[j] = apply_activation(x, ep.act);
+                }
+            }
+            if (full_chunk) {
+                uint4* dst = reinterpret_cast<uint4*>(drow + col0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]), p1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
+                    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]), p3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
+                    uint4 u;
+                    u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
+                    u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
+                    dst[q] = u;
+                }
+            } else {
+                for (int j = 0; j < 32; ++j) if (col0 + j < N) drow[col0 + j] = __float2bfloat16_rn(v[j]);
+            }
+        }
+    };
+    uint32_t r0[32], r1[32];
+    tmem_ld_32x32(acc_addr, r0);
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; c += 2) {
+        tmem_ld_wait();
+        tmem_ld_32x32(acc_addr + (c + 1) * 32, r1);
+        chunk(r0, c);
+        __syncwarp();
+        tmem_ld_wait();
+        if (c + 2 < BN / 32) tmem_ld_32x32(acc_addr + (c + 2) * 32, r0);
+        chunk(r1, c + 1);
+        __syncwarp();
+    }
 }
 
 template <int BN, int STAGES, bool B_KMAJOR>
@@ -148,83 +231,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int n0 = tn * BN;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase, status, 0x34)) break;
             tc_fence_after();
-            const float rs = (ep.row_scale && row < M) ? ep.row_scale[row] : 1.0f;
-            __nv_bfloat16* drow = ep.D + static_cast<size_t>(row) * N;
-            const uint32_t acc_addr = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * BN;
-            // One 32-column chunk; the next chunk's TMEM load is already in flight while this one is computed.
-            auto chunk = [&](const uint32_t (&r)[32], int c) {
-                const int col0 = n0 + c * 32;  // warp-uniform
-                if (col0 >= N || row >= M) return;
-                {
-                    float v[32];
-                    const bool full_chunk = vec_ok && col0 + 32 <= N;
-                    if (full_chunk) {  // scales and bias as 16-byte loads: every lane reads the same 128 / 64 bytes (broadcast)
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * rs;
-                        if (ep.col_scale) {
-#pragma unroll
-                            for (int q = 0; q < 8; ++q) {
-                                const float4 c4 = __ldg(reinterpret_cast<const float4*>(ep.col_scale + col0) + q);
-                                v[q * 4 + 0] *= c4.x; v[q * 4 + 1] *= c4.y; v[q * 4 + 2] *= c4.z; v[q * 4 + 3] *= c4.w;
-                            }
-                        }
-                        if (ep.bias) {
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const uint4 u = __ldg(reinterpret_cast<const uint4*>(ep.bias + col0) + q);
-                                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                                for (int t = 0; t < 4; ++t) { v[q * 8 + 2 * t] += __uint_as_float(w[t] << 16); v[q * 8 + 2 * t + 1] += __uint_as_float(w[t] & 0xffff0000u); }
-                            }
-                        }
-                        if (ep.act == PYC_B200_ACT_GELU) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 2) gelu_erf_x2(v[j], v[j + 1]);
-                        } else if (ep.act == PYC_B200_ACT_RELU) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int col = col0 + j;
-                            float x = __uint_as_float(r[j]) * rs;
-                            if (col < N) {
-                                if (ep.col_scale) x *= __ldg(ep.col_scale + col);
-                                if (ep.bias) x += __bfloat162float(ep.bias[col]);
-                            }
-                            v[j] = apply_activation(x, ep.act);
-                        }
-                    }
-                    if (full_chunk) {
-                        uint4* dst = reinterpret_cast<uint4*>(drow + col0);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]), p1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]), p3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
-                            uint4 u;
-                            u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
-                            u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
-                            dst[q] = u;
-                        }
-                    } else {
-                        for (int j = 0; j < 32; ++j) if (col0 + j < N) drow[col0 + j] = __float2bfloat16_rn(v[j]);
-                    }
-                }
-            };
-            uint32_t r0[32], r1[32];
-            tmem_ld_32x32(acc_addr, r0);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; c += 2) {
-                tmem_ld_wait();
-                tmem_ld_32x32(acc_addr + (c + 1) * 32, r1);
-                chunk(r0, c);
-                __syncwarp();
-                tmem_ld_wait();
-                if (c + 2 < BN / 32) tmem_ld_32x32(acc_addr + (c + 2) * 32, r0);
-                chunk(r1, c + 1);
-                __syncwarp();
-            }
+            fp8_epilogue_tile<BN>(ep, tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * BN, row, n0, M, N, vec_ok);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
@@ -262,6 +269,177 @@ int launch_fp8_instance(int M, int N, int K, const void* A, const void* B, const
     return 0;
 }
 
+
+// ---------------------------------------------------------------------------------------
+// CTA-pair form (cta_group::2, 256 x 256 x 32 per instruction), the fp8 twin of the bf16 pair
+// kernel: a pair owns a 256 x 256 tile, each CTA loads its 128 A rows and HALF of the B tile
+// (32 KB per stage instead of 48 KB, ring 7 deep), the leader's single thread issues for both
+// tensor cores, loads of both CTAs count on the leader's "full" barrier, epilogue warps of both
+// CTAs release the accumulator on the leader's barrier.  No multicast of any kind.
+// ---------------------------------------------------------------------------------------
+constexpr int PBN = 256, PBNH = 128;
+constexpr int PB_STAGE_BYTES = PBNH * BK;     // 16 KB
+constexpr int P_GROUP_M = 8;                  // in pair tiles (8 x 256 rows)
+
+__device__ __forceinline__ void fp8_pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int group = P_GROUP_M * tiles_n;
+    const int g = tile / group;
+    const int first = g * P_GROUP_M;
+    const int gm = min(P_GROUP_M, tiles_m - first);
+    const int local = tile - g * group;
+    tm = first + local % gm;
+    tn = local / gm;
+}
+
+template <int STAGES, bool B_KMAJOR>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Fp8Epilogue ep, int M, int N, int K, int* status) {
+    constexpr uint32_t PAIR_TX = 2 * (A_STAGE_BYTES + PB_STAGE_BYTES);
+    constexpr uint32_t TMEM_COLS = 2 * PBN;
+    constexpr uint32_t IDESC = make_idesc(0, 0, 0, B_KMAJOR ? 0 : 1, 2 * BM, PBN);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * PB_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + PBN - 1) / PBN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 8); }  // 4 epilogue warps x 2 CTAs
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) { tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish_pair(); }
+    tc_fence_before();
+    cluster_sync_all();   // barriers of both CTAs exist before anyone signals across the pair
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t leader_full0 = map_to_cta(full0, 0);
+            const uint32_t a_dst0 = smem_u32(sA), b_dst0 = smem_u32(sB);
+            uint32_t stage = 0, phase = 0, a_dst = a_dst0, b_dst = b_dst0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
+                int tm, tn;
+                fp8_pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                const int m0 = tm * 2 * BM + static_cast<int>(rank) * BM;
+                const int n0 = tn * PBN + static_cast<int>(rank) * PBNH;
+                for (int kb = 0, k0 = 0; kb < num_kb; ++kb, k0 += BK) {
+                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, status, 0x35)) { ok = false; break; }
+                    const uint32_t leader_full = leader_full0 + 8 * stage;
+                    if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * stage, PAIR_TX);
+                    tma_load_2d_pair(a_dst, &tmA, leader_full, k0, m0);
+                    if (B_KMAJOR) tma_load_2d_pair(b_dst, &tmB, leader_full, k0, n0);
+                    else tma_load_2d_pair(b_dst, &tmB, leader_full, n0, k0);
+                    a_dst += A_STAGE_BYTES; b_dst += PB_STAGE_BYTES;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; a_dst = a_dst0; b_dst = b_dst0; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {  // the pair's single MMA issuer
+            constexpr uint32_t DESC_HI = smem_desc_hi_sw128(1024);
+            constexpr uint32_t A_STEP = A_STAGE_BYTES >> 4, B_STEP = PB_STAGE_BYTES >> 4;
+            constexpr uint32_t A_K32 = 32 >> 4, B_K32 = (B_KMAJOR ? 32 : 32 * 128) >> 4;
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(sA), 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(sB), B_KMAJOR ? 16 : BK * 128);
+            const uint32_t empty_peer0 = map_to_cta(empty0, 1), tfull_peer0 = map_to_cta(tfull0, 1);
+            uint32_t stage = 0, phase = 0, a_lo = a_lo0, b_lo = b_lo0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++it) {
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, status, 0x36)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * PBN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8 * stage, phase, status, 0x37)) { ok = false; break; }
+                    tc_fence_after();
+                    umma_f8_pair(d_tmem, smem_desc_join(a_lo, DESC_HI), smem_desc_join(b_lo, DESC_HI), IDESC, kb != 0 ? 1u : 0u);
+#pragma unroll
+                    for (uint32_t k4 = 1; k4 < BK / 32; ++k4)
+                        umma_f8_pair(d_tmem, smem_desc_join(a_lo + k4 * A_K32, DESC_HI), smem_desc_join(b_lo + k4 * B_K32, DESC_HI), IDESC, 1u);
+                    umma_commit_pair(empty0 + 8 * stage);
+                    umma_commit_pair(empty_peer0 + 8 * stage);
+                    a_lo += A_STEP; b_lo += B_STEP;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
+                }
+                if (ok) {
+                    umma_commit_pair(tfull0 + 8 * acc);
+                    umma_commit_pair(tfull_peer0 + 8 * acc);
+                }
+            }
+        }
+    } else {
+        const int wq = warp & 3;
+        const uint32_t tempty_leader0 = map_to_cta(tempty0, 0);
+        const bool vec_ok = (N % 8 == 0) && (reinterpret_cast<uintptr_t>(ep.D) % 16 == 0) &&
+                            (reinterpret_cast<uintptr_t>(ep.col_scale) % 16 == 0) && (reinterpret_cast<uintptr_t>(ep.bias) % 16 == 0);
+        int it = 0;
+        for (int tile = pair; tile < num_tiles; tile += pairs, ++it) {
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            int tm, tn;
+            fp8_pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int row = tm * 2 * BM + static_cast<int>(rank) * BM + wq * 32 + lane;
+            const int n0 = tn * PBN;
+            if (!mbar_wait(tfull0 + 8 * acc, acc_phase, status, 0x38)) break;
+            tc_fence_after();
+            fp8_epilogue_tile<PBN>(ep, tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * PBN, row, n0, M, N, vec_ok);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * acc);
+        }
+    }
+
+    // Both CTAs meet here (also after a timed-out wait): neither exits while the other may still signal its barriers
+    // or read its shared memory.
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        if (*reinterpret_cast<volatile int*>(status) != ST_OK) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int STAGES, bool B_KMAJOR>
+int launch_fp8_pair_instance(int M, int N, int K, const void* A, const void* B, const Fp8Epilogue& ep, cudaStream_t stream, int* status) {
+    auto kernel = gemm_fp8_pair_kernel<STAGES, B_KMAJOR>;
+    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + PB_STAGE_BYTES) + (2 * STAGES + 4) * 8 + 16;
+    static bool attr_set[16] = {};
+    int dev = 0;
+    B200_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 16 && !attr_set[dev]) {
+        B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        attr_set[dev] = true;
+    }
+    CUtensorMap tmA, tmB;
+    if (encode_tmap_2d(&tmA, A, 1, M, K, static_cast<uint64_t>(K), BM, BK) != 0) return -1;
+    if (B_KMAJOR) { if (encode_tmap_2d(&tmB, B, 1, N, K, static_cast<uint64_t>(K), PBNH, BK) != 0) return -1; }
+    else { if (encode_tmap_2d(&tmB, B, 1, K, N, static_cast<uint64_t>(N), BK, 128) != 0) return -1; }
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + PBN - 1) / PBN);
+    const int max_pairs = sm_count() / 2;
+    const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
+    kernel<<<grid, 192, smem, stream>>>(tmA, tmB, ep, M, N, K, status);
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
 }  // namespace
 
 int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col_major, const float* row_scale, const float* col_scale,
@@ -276,6 +454,11 @@ int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col
     const int sms = sm_count();
     const long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256), t128 = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
     const bool use256 = ((t256 + sms - 1) / sms) * 256 <= ((t128 + sms - 1) / sms) * 128 * 1.15;
+    // CTA pairs once there is at least a wave of 256 x 256 tiles (PYC_B200_FP8_PAIR=0: never, =1: always)
+    const char* pe = getenv("PYC_B200_FP8_PAIR");
+    const long long pair_tiles = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
+    if (pe && (pe[0] == '0' || pe[0] == '1') ? pe[0] == '1' : pair_tiles >= sms / 2)
+        return b_col_major ? launch_fp8_pair_instance<7, true>(M, N, K, A, B, ep, stream, status) : launch_fp8_pair_instance<7, false>(M, N, K, A, B, ep, stream, status);
     if (use256) return b_col_major ? launch_fp8_instance<256, 4, true>(M, N, K, A, B, ep, stream, status) : launch_fp8_instance<256, 4, false>(M, N, K, A, B, ep, stream, status);
     return b_col_major ? launch_fp8_instance<128, 6, true>(M, N, K, A, B, ep, stream, status) : launch_fp8_instance<128, 6, false>(M, N, K, A, B, ep, stream, status);
 }

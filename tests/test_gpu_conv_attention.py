@@ -88,9 +88,9 @@ def attn_case(backend, oracle_lib, dtype, bh, seq, d, causal, seed=0, symbol=Non
     assert err <= (tol or TOL[dtype]), f"attention bh={bh} seq={seq} d={d} causal={causal}: rel err {err:.3e}"
 
 
-@pytest.fixture(params=["1", "2"], ids=["kernel1_smemP", "kernel2_tmemP"])
+@pytest.fixture(params=["1", "2", "3"], ids=["kernel1_smemP", "kernel2_tmemP", "kernel3_persistent"])
 def attn_kernel(request, monkeypatch):
-    # both tensor-core kernels are held to the same bar; the env switch picks one
+    # all tensor-core kernels are held to the same bar; the env switch picks one
     monkeypatch.setenv("PYC_B200_ATTENTION_KERNEL", request.param)
     return request.param
 
@@ -107,6 +107,14 @@ def test_attention_tc_d64_f16_and_symbols(backend, oracle_lib, attn_kernel):
     attn_case(backend, oracle_lib, abi.DTYPE_BF16, 1, 256, 128, True, seed=3, symbol="b200_attention_bf16_causal")
     attn_case(backend, oracle_lib, abi.DTYPE_F16, 1, 256, 128, False, seed=4, symbol="cutlass_attention_f16")
     assert backend.load().pyc_cutlass_attention_dispatch(b"nope", 8, 8, None, None, None, None, 1.0, None) == -1
+
+
+def test_attention_persistent_ctas_walk_several_query_blocks(backend, oracle_lib):
+    # more work units than the 2 x 148 resident CTAs of the default (persistent) kernel, so CTAs go round their loop more
+    # than once: barriers, TMEM and the K/V ring carry over from one query block to the next
+    attn_case(backend, oracle_lib, abi.DTYPE_BF16, 75, 512, 128, False, seed=21)    # 300 single-block units
+    attn_case(backend, oracle_lib, abi.DTYPE_BF16, 160, 384, 64, True, seed=22)     # 320 units: pairs (2, 0) and the lone middle block
+    attn_case(backend, oracle_lib, abi.DTYPE_F16, 70, 520, 128, True, seed=23)      # ragged: 5 query blocks, last one 8 rows
 
 
 def test_attention_row_warp_paths(backend, oracle_lib):
