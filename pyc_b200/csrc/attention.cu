@@ -979,10 +979,10 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
     // the second made persistent.
     const char* pick = getenv("PYC_B200_ATTENTION_KERNEL");
     const bool first = pick && pick[0] == '1';
-    // Without a choice from the environment: causal work (query blocks of very different length, many short ones) goes to the
-    // persistent kernel; non-causal work, where every CTA runs the same long loop, is a few per cent faster with one CTA per
-    // query block (measured at 2048 and 8192 keys).
-    const bool second = pick ? pick[0] == '2' : !causal;
+    // Without a choice from the environment: causal work up to 4096 keys (query blocks of very different length, many short
+    // ones) goes to the persistent kernel, 2-13 % faster there; long or non-causal work, where every CTA runs the same long
+    // loop, is 2-5 % faster with one CTA per query block (measured at 2048, 4096 and 8192 keys).
+    const bool second = pick ? pick[0] == '2' : !(causal && seq <= 4096);
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
     CUtensorMap tq, tk, tv;
