@@ -13,6 +13,7 @@
 // Replaces the same PyC code as gemm_tc.cu (cutlass_kernels/gemm/kernel.cu:48-84).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <stdlib.h>
 
 #include "internal.h"
 #include "math.cuh"
@@ -34,6 +35,7 @@ struct Epi2 {
     const void* add;
     float alpha, add_scale;
     int add_mode, act, vec_ok;
+    int l2_hints;   // 0: none; 1: A panel evict_last, B evict_first; 2: both evict_last; 3: A evict_last only
 };
 
 template <int FMT> struct El;
@@ -108,6 +110,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (lane == 0) {  // each CTA loads its own halves; bytes are counted on the leader's barrier
             const uint32_t leader_full0 = map_to_cta(full0, 0);
             const uint32_t a_dst0 = smem_u32(sA), b_dst0 = smem_u32(sB);
+            // The tile order keeps a panel of A rows and sweeps B across it: A is what the next wave wants to find in L2.
+            const uint64_t pol_a = l2_policy_evict_last();
+            const uint64_t pol_b = ep.l2_hints == 2 ? l2_policy_evict_last() : l2_policy_evict_first();
             uint32_t stage = 0, phase = 0, a_dst = a_dst0, b_dst = b_dst0;
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
@@ -119,12 +124,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, status, 0x41)) { ok = false; break; }
                     const uint32_t leader_full = leader_full0 + 8 * stage;
                     if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * stage, PAIR_TX);
-                    tma_load_2d_pair(a_dst, &tmA, leader_full, k0, m0);
-                    if (B_KMAJOR) {
-                        tma_load_2d_pair(b_dst, &tmB, leader_full, k0, n0);
+                    if (ep.l2_hints) {
+                        tma_load_2d_pair_hint(a_dst, &tmA, leader_full, k0, m0, pol_a);
+                        if (B_KMAJOR) {
+                            if (ep.l2_hints == 3) tma_load_2d_pair(b_dst, &tmB, leader_full, k0, n0);
+                            else tma_load_2d_pair_hint(b_dst, &tmB, leader_full, k0, n0, pol_b);
+                        } else if (ep.l2_hints == 3) {
+                            tma_load_2d_pair(b_dst, &tmB, leader_full, n0, k0);
+                            tma_load_2d_pair(b_dst + BK * 128, &tmB, leader_full, n0 + 64, k0);
+                        } else {
+                            tma_load_2d_pair_hint(b_dst, &tmB, leader_full, n0, k0, pol_b);
+                            tma_load_2d_pair_hint(b_dst + BK * 128, &tmB, leader_full, n0 + 64, k0, pol_b);
+                        }
                     } else {
-                        tma_load_2d_pair(b_dst, &tmB, leader_full, n0, k0);
-                        tma_load_2d_pair(b_dst + BK * 128, &tmB, leader_full, n0 + 64, k0);
+                        tma_load_2d_pair(a_dst, &tmA, leader_full, k0, m0);
+                        if (B_KMAJOR) {
+                            tma_load_2d_pair(b_dst, &tmB, leader_full, k0, n0);
+                        } else {
+                            tma_load_2d_pair(b_dst, &tmB, leader_full, n0, k0);
+                            tma_load_2d_pair(b_dst + BK * 128, &tmB, leader_full, n0 + 64, k0);
+                        }
                     }
                     a_dst += A_STAGE; b_dst += B_STAGE;
                     if (++stage == STAGES) { stage = 0; phase ^= 1; a_dst = a_dst0; b_dst = b_dst0; }
@@ -283,6 +302,8 @@ int launch_pair_instance(const GemmProblem& p, cudaStream_t stream, int* status)
     ep.vec_ok = ((reinterpret_cast<uintptr_t>(p.D) % 16 == 0) && (p.N % 8 == 0) &&
                  (ep.add_mode == PYC_B200_ADD_NONE || ep.add_mode == PYC_B200_ADD_SCALAR || reinterpret_cast<uintptr_t>(p.add) % 16 == 0)) ? 1 : 0;
     if (ep.vec_ok && reinterpret_cast<uintptr_t>(p.D) % 32 == 0 && p.N % 16 == 0) ep.vec_ok = 2;   // rows start on 32-byte boundaries
+    ep.l2_hints = 0;
+    if (const char* h = getenv("PYC_B200_GEMM_L2_HINTS")) { const int v = atoi(h); if (v >= 0 && v <= 3) ep.l2_hints = v; }
     const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
     const int max_pairs = sm_count() / 2;
     const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
