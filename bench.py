@@ -27,7 +27,7 @@ ALGO_BYTES = 3 * M * N * 2 + N * 2          # A, B, D bf16 + bias
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this exact shape, from the ncu capture summarised in
 # profiles/gemm_tc_bf16_8192x8192x8192_traffic.md (the CTA-pair kernel the dispatch picks for this shape; update both together
 # when the kernel changes).
-NCU_TRAFFIC_BYTES = 1066646784 + 125710336
+NCU_TRAFFIC_BYTES = 1104316160 + 126199296
 METRIC = "fused bf16 GEMM+bias+GELU TFLOP/s via pyc_cuda_dispatch"
 
 
