@@ -205,6 +205,31 @@ typedef struct {
 size_t pyc_b200_ffn_workspace_bytes(int tokens, int hidden, int inner);
 int pyc_b200_ffn_block(const pyc_b200_ffn_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Tensor-parallel FFN without a library collective: the reduce-scatter is done by the second GEMM's epilogue and the
+ * all-gather by the reduction kernel, both with plain stores into peer memory over NVLink.
+ *   - every rank owns tokens / world consecutive rows of the result and a receive buffer [world][tokens/world][hidden]
+ *     bf16 that the other ranks can write (pyc_b200_symm_alloc + pyc_b200_symm_open, or any peer-mapped memory);
+ *   - pyc_b200_ffn_block_scatter is pyc_b200_ffn_block whose last GEMM stores row r of this rank's partial sum into slot
+ *     `rank` of the receive buffer of the rank that owns r (recv_slots[owner]); args->out is not written and may be NULL;
+ *   - after ALL ranks have finished that call (a barrier of the caller: an NCCL barrier on the stream, for instance),
+ *     pyc_b200_tp_reduce_broadcast adds the world slots of the local receive buffer in fp32 and stores the owned rows,
+ *     rounded to bf16, into the [tokens][hidden] output of every rank (outs[0..world-1]); after a second barrier every
+ *     rank holds the full result.
+ * No kernel waits on another GPU; ordering between ranks is the caller's two barriers.  world <= PYC_B200_TP_MAX_RANKS.
+ * PyC has no counterpart: its options carry world_size/rank (include/pyc/compiler_api.h:53-62) but pyc_run_model never
+ * exchanges data between ranks. */
+#define PYC_B200_TP_MAX_RANKS 8
+int pyc_b200_ffn_block_scatter(const pyc_b200_ffn_args* args, void* workspace, size_t workspace_bytes, void* const* recv_slots,
+                               int world, int rank, void* stream);
+int pyc_b200_tp_reduce_broadcast(const void* recv_local, void* const* outs, int world, int rank, int rows_per_rank, int hidden,
+                                 void* stream);
+/* Device memory that other processes on the same node can map: allocate + export a 64-byte handle, open a peer's handle,
+ * close it again, free the own allocation.  (cudaMalloc + CUDA IPC; the handle is sent by whatever channel the caller has.) */
+int pyc_b200_symm_alloc(size_t bytes, void** ptr, unsigned char handle[64]);
+int pyc_b200_symm_open(const unsigned char handle[64], void** ptr);
+int pyc_b200_symm_close(void* ptr);
+int pyc_b200_symm_free(void* ptr);
+
 /* Time every registered tile configuration for (dtype, M, N, K) with CUDA
  * events, feed the measured milliseconds to PyC's registry
  * (pyc_kernel_benchmark_update_symbol) when it is linked, remember the winner

@@ -21,7 +21,8 @@ EXPORTS = [
     # additive
     "pyc_b200_gemm", "pyc_b200_gemm_static", "pyc_b200_add", "pyc_b200_bias_act", "pyc_b200_layernorm", "pyc_b200_softmax",
     "pyc_b200_reduce_sum", "pyc_b200_quantize_rows", "pyc_b200_layernorm_quantize", "pyc_b200_gemm_fp8",
-    "pyc_b200_ffn_workspace_bytes", "pyc_b200_ffn_block", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm",
+    "pyc_b200_ffn_workspace_bytes", "pyc_b200_ffn_block", "pyc_b200_ffn_block_scatter", "pyc_b200_tp_reduce_broadcast",
+    "pyc_b200_symm_alloc", "pyc_b200_symm_open", "pyc_b200_symm_close", "pyc_b200_symm_free", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm",
     "pyc_b200_get_runtime_info", "pyc_b200_set_stream", "pyc_b200_device_status", "pyc_b200_last_error",
     "pyc_b200_shutdown",
 ]
@@ -66,6 +67,12 @@ def load():
     L.pyc_b200_ffn_workspace_bytes.argtypes = [i, i, i]
     L.pyc_b200_ffn_workspace_bytes.restype = sz
     L.pyc_b200_ffn_block.argtypes = [C.POINTER(abi.FfnArgs), vp, sz, vp]
+    L.pyc_b200_ffn_block_scatter.argtypes = [C.POINTER(abi.FfnArgs), vp, sz, C.POINTER(vp), i, i, vp]
+    L.pyc_b200_tp_reduce_broadcast.argtypes = [vp, C.POINTER(vp), i, i, i, i, vp]
+    L.pyc_b200_symm_alloc.argtypes = [sz, C.POINTER(vp), C.c_char_p]
+    L.pyc_b200_symm_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    L.pyc_b200_symm_close.argtypes = [vp]
+    L.pyc_b200_symm_free.argtypes = [vp]
     L.pyc_b200_attention.argtypes = [i, i, i, i, vp, vp, vp, vp, f, i, vp]
     L.pyc_b200_conv2d.argtypes = [i] * 12 + [vp, vp, vp, i, vp, vp]
     L.pyc_b200_autotune_gemm.argtypes = [i, i, i, i, i, C.c_char_p, sz, C.POINTER(C.c_double)]
@@ -193,6 +200,53 @@ def ffn_block(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, out, workspa
     a.w2, a.w2_scale, a.b2 = w2, w2_scale, b2
     a.out = out
     _check(load().pyc_b200_ffn_block(C.byref(a), workspace, workspace_bytes, stream), "pyc_b200_ffn_block")
+
+
+def _ffn_args(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, out, ln_gamma, ln_beta, b1, b2, eps):
+    a = abi.FfnArgs()
+    a.tokens, a.hidden, a.inner = tokens, hidden, inner
+    a.x, a.ln_gamma, a.ln_beta, a.eps = x, ln_gamma, ln_beta, eps
+    a.w1, a.w1_scale, a.b1 = w1, w1_scale, b1
+    a.w2, a.w2_scale, a.b2 = w2, w2_scale, b2
+    a.out = out
+    return a
+
+
+def ffn_block_scatter(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, workspace, workspace_bytes, recv_slots, rank,
+                      ln_gamma=None, ln_beta=None, b1=None, b2=None, eps=1e-5, stream=0):
+    """The FFN block whose last GEMM stores every row into slot `rank` of the owning rank's receive buffer (recv_slots[owner])."""
+    a = _ffn_args(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, None, ln_gamma, ln_beta, b1, b2, eps)
+    world = len(recv_slots)
+    table = (C.c_void_p * world)(*recv_slots)
+    _check(load().pyc_b200_ffn_block_scatter(C.byref(a), workspace, workspace_bytes, table, world, rank, stream), "pyc_b200_ffn_block_scatter")
+
+
+def tp_reduce_broadcast(recv_local, outs, rank, rows_per_rank, hidden, stream=0):
+    world = len(outs)
+    table = (C.c_void_p * world)(*outs)
+    _check(load().pyc_b200_tp_reduce_broadcast(recv_local, table, world, rank, rows_per_rank, hidden, stream), "pyc_b200_tp_reduce_broadcast")
+
+
+def symm_alloc(nbytes):
+    """(device pointer, 64-byte handle another process of this node can open)"""
+    ptr = C.c_void_p()
+    handle = C.create_string_buffer(64)
+    _check(load().pyc_b200_symm_alloc(nbytes, C.byref(ptr), handle), "pyc_b200_symm_alloc")
+    return ptr.value, handle.raw
+
+
+def symm_open(handle):
+    ptr = C.c_void_p()
+    _check(load().pyc_b200_symm_open(handle, C.byref(ptr)), "pyc_b200_symm_open")
+    return ptr.value
+
+
+def symm_close(ptr):
+    _check(load().pyc_b200_symm_close(ptr), "pyc_b200_symm_close")
+
+
+def symm_free(ptr):
+    _check(load().pyc_b200_symm_free(ptr), "pyc_b200_symm_free")
 
 
 def attention(dtype, batch_heads, seq, d, q, k, v, out, scale, causal, stream=0):

@@ -33,6 +33,11 @@ struct Fp8Epilogue {
     const float* col_scale;   // [N] or null
     const __nv_bfloat16* bias;  // [N] or null
     int act;
+    // Row scatter for tensor parallelism (world > 0): row r of D belongs to rank r / rows_per_rank and is stored at
+    // dst[owner] + (src_rank * rows_per_rank + r % rows_per_rank) * N, i.e. straight into the owner's receive slot for this
+    // rank (its own memory or a peer's, mapped into this process); D is unused then.
+    __nv_bfloat16* dst[PYC_B200_TP_MAX_RANKS];
+    int world, rows_per_rank, src_rank;
 };
 
 __device__ __forceinline__ void fp8_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -51,6 +56,10 @@ template <int BN>
 __device__ __forceinline__ void fp8_epilogue_tile(const Fp8Epilogue& ep, uint32_t acc_addr, int row, int n0, int M, int N, bool vec_ok) {
     const float rs = (ep.row_scale && row < M) ? ep.row_scale[row] : 1.0f;
     __nv_bfloat16* drow = ep.D + static_cast<size_t>(row) * N;
+    if (ep.world > 0 && row < M) {
+        const int owner = row / ep.rows_per_rank;
+        drow = ep.dst[owner] + (static_cast<size_t>(ep.src_rank) * ep.rows_per_rank + (row - owner * ep.rows_per_rank)) * N;
+    }
     // One 32-column chunk; the next chunk's TMEM load is already in flight while this one is computed.
     auto chunk = [&](const uint32_t (&r)[32], int c) {
         const int col0 = n0 + c * 32;  // warp-uniform
@@ -443,14 +452,26 @@ int launch_fp8_pair_instance(int M, int N, int K, const void* A, const void* B, 
 }  // namespace
 
 int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col_major, const float* row_scale, const float* col_scale,
-                    const void* bias, int act, void* D, cudaStream_t stream, int* status) {
-    if (M <= 0 || N <= 0 || K <= 0 || !A || !B || !D || !status) { set_error("fp8 gemm: bad shape or NULL pointer"); return -1; }
+                    const void* bias, int act, void* D, cudaStream_t stream, int* status, const Fp8Scatter* scatter) {
+    if (M <= 0 || N <= 0 || K <= 0 || !A || !B || (!D && !scatter) || !status) { set_error("fp8 gemm: bad shape or NULL pointer"); return -1; }
+    if (scatter && (scatter->world < 1 || scatter->world > PYC_B200_TP_MAX_RANKS || scatter->rank < 0 || scatter->rank >= scatter->world ||
+                    M % scatter->world != 0)) { set_error("fp8 gemm: bad scatter description (world %d, rank %d, M %d)", scatter->world, scatter->rank, M); return -1; }
     if (K % 16 != 0 || (!b_col_major && N % 16 != 0) || reinterpret_cast<uintptr_t>(A) % 16 || reinterpret_cast<uintptr_t>(B) % 16) {
         set_error("fp8 gemm: needs K %% 16 == 0, N %% 16 == 0 for row-major B and 16-byte aligned operands (TMA)"); return -1;
     }
     Fp8Epilogue ep;
     ep.D = static_cast<__nv_bfloat16*>(D); ep.row_scale = row_scale; ep.col_scale = col_scale;
     ep.bias = static_cast<const __nv_bfloat16*>(bias); ep.act = act;
+    ep.world = 0; ep.rows_per_rank = 0; ep.src_rank = 0;
+    for (int i = 0; i < PYC_B200_TP_MAX_RANKS; ++i) ep.dst[i] = nullptr;
+    if (scatter) {
+        ep.world = scatter->world; ep.rows_per_rank = M / scatter->world; ep.src_rank = scatter->rank;
+        for (int i = 0; i < scatter->world; ++i) {
+            if (!scatter->dst[i] || reinterpret_cast<uintptr_t>(scatter->dst[i]) % 16) { set_error("fp8 gemm: scatter slot %d is NULL or not 16-byte aligned", i); return -1; }
+            ep.dst[i] = static_cast<__nv_bfloat16*>(scatter->dst[i]);
+        }
+        if (!ep.D) ep.D = ep.dst[scatter->rank];   // only its alignment is looked at
+    }
     const int sms = sm_count();
     const long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256), t128 = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
     const bool use256 = ((t256 + sms - 1) / sms) * 256 <= ((t128 + sms - 1) / sms) * 128 * 1.15;

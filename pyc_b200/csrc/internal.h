@@ -102,6 +102,14 @@ int launch_conv2d(pyc_dtype dt, int N, int H, int W, int C, int K, int R, int S,
                   int stride_h, int stride_w, const void* in, const void* filt, const void* bias, int relu,
                   void* out, cudaStream_t s, int* status);
 
+// ---- fp8 GEMM (+ row scatter for tensor parallelism) / row quantisers --------------
+struct Fp8Scatter {
+    void* dst[PYC_B200_TP_MAX_RANKS];   // receive buffer of every rank: [world][M / world][N] bf16
+    int world, rank;
+};
+int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col_major, const float* row_scale, const float* col_scale,
+                    const void* bias, int act, void* D, cudaStream_t stream, int* status, const Fp8Scatter* scatter = nullptr);
+
 // ---- registry -------------------------------------------------------------------
 void registry_init_once();
 int registry_count(const char* op_key);

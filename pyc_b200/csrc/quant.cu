@@ -13,8 +13,6 @@
 #include "internal.h"
 
 namespace b200 {
-int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col_major, const float* row_scale, const float* col_scale,
-                    const void* bias, int act, void* D, cudaStream_t stream, int* status);
 
 namespace {
 
@@ -167,8 +165,8 @@ size_t pyc_b200_ffn_workspace_bytes(int tokens, int hidden, int inner) {
     return align256(T * H) + align256(T * 4) + align256(T * I * 2) + align256(T * I) + align256(T * 4);
 }
 
-int pyc_b200_ffn_block(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* stream) {
-    if (!a || !a->x || !a->w1 || !a->w2 || !a->w1_scale || !a->w2_scale || !a->out || !workspace) { set_error("ffn: NULL argument"); return -1; }
+static int ffn_block_impl(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* stream, const b200::Fp8Scatter* scatter) {
+    if (!a || !a->x || !a->w1 || !a->w2 || !a->w1_scale || !a->w2_scale || (!a->out && !scatter) || !workspace) { set_error("ffn: NULL argument"); return -1; }
     const size_t need = pyc_b200_ffn_workspace_bytes(a->tokens, a->hidden, a->inner);
     if (need == 0 || workspace_bytes < need) { set_error("ffn: workspace of %zu bytes needed, %zu given", need, workspace_bytes); return -1; }
     if (reinterpret_cast<uintptr_t>(workspace) % 256) { set_error("ffn: workspace must be 256-byte aligned"); return -1; }
@@ -183,12 +181,27 @@ int pyc_b200_ffn_block(const pyc_b200_ffn_args* a, void* workspace, size_t works
     int* st = device_status_word();
     if (!st) return -1;
     // 1. LayerNorm + per-token quantisation   2. fp8 GEMM1 (+bias) + GELU -> bf16
-    // 3. per-token quantisation               4. fp8 GEMM2 (+bias) -> bf16 (a partial sum when the inner dimension is sharded)
+    // 3. per-token quantisation               4. fp8 GEMM2 (+bias) -> bf16 (a partial sum when the inner dimension is sharded;
+    //                                            with `scatter`, every row goes straight to the receive slot of the rank that owns it)
     if (launch_rowquant<true>(a->x, a->ln_gamma, a->ln_beta, xq, xs, T, H, a->eps > 0.0f ? a->eps : 1e-5f, s) != 0) return -1;
     if (launch_gemm_fp8(a->tokens, a->inner, a->hidden, xq, a->w1, 0, xs, a->w1_scale, a->b1, PYC_B200_ACT_GELU, h, s, st) != 0) return -1;
     if (launch_rowquant<false>(h, nullptr, nullptr, hq, hs, T, I, 0.0f, s) != 0) return -1;
-    if (launch_gemm_fp8(a->tokens, a->hidden, a->inner, hq, a->w2, 0, hs, a->w2_scale, a->b2, PYC_B200_ACT_NONE, a->out, s, st) != 0) return -1;
+    if (launch_gemm_fp8(a->tokens, a->hidden, a->inner, hq, a->w2, 0, hs, a->w2_scale, a->b2, PYC_B200_ACT_NONE, a->out, s, st, scatter) != 0) return -1;
     return 0;
+}
+
+int pyc_b200_ffn_block(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* stream) {
+    return ffn_block_impl(a, workspace, workspace_bytes, stream, nullptr);
+}
+
+int pyc_b200_ffn_block_scatter(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* const* recv_slots, int world, int rank,
+                               void* stream) {
+    if (!recv_slots || world < 1 || world > PYC_B200_TP_MAX_RANKS || rank < 0 || rank >= world) { set_error("ffn scatter: bad world/rank or NULL slot table"); return -1; }
+    if (a && a->tokens % world != 0) { set_error("ffn scatter: %d tokens do not split over %d ranks", a->tokens, world); return -1; }
+    b200::Fp8Scatter sc;
+    sc.world = world; sc.rank = rank;
+    for (int i = 0; i < PYC_B200_TP_MAX_RANKS; ++i) sc.dst[i] = i < world ? recv_slots[i] : nullptr;
+    return ffn_block_impl(a, workspace, workspace_bytes, stream, &sc);
 }
 
 }  // extern "C"

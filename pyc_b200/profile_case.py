@@ -37,6 +37,7 @@ def main():
     ap.add_argument("--epilogue", default="bias_gelu", choices=["none", "bias_relu", "bias_gelu"])
     ap.add_argument("--tokens", type=int, default=8192); ap.add_argument("--hidden", type=int, default=4096); ap.add_argument("--inner", type=int, default=16384)
     ap.add_argument("--chunks", type=int, default=None, help="ffn: row slices whose all-reduce overlaps the next slice (default: 4 when tensor parallel)")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"], help="ffn under torchrun: NCCL all-reduce or stores into peer memory")
     ap.add_argument("--symbol", default=None)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=1)
@@ -98,10 +99,18 @@ def main():
         from . import ffn
         xb, w1, s1, w2, s2 = workloads.ffn_inputs(a.tokens, a.hidden, a.inner)
         w1r, s1r, w2r = ffn.shard_weights(w1, s1, w2, rank, world)
-        blk = ffn.FfnBlock(a.tokens, a.hidden, a.inner // world, w1r, s1r, w2r, s2, torch, chunks=a.chunks)
+        blk = ffn.FfnBlock(a.tokens, a.hidden, a.inner // world, w1r, s1r, w2r, s2, torch, chunks=a.chunks, exchange=a.exchange)
         X = torch.from_numpy(xb.view(np.int16)).cuda()
         run = lambda: blk.run(X)
         work = ("TFLOP/s (whole block, all ranks)", 4.0 * a.tokens * a.hidden * a.inner / 1e12)
+        if world > 1 and a.exchange == "peer":
+            # same inputs through the NCCL variant: the two exchanges must agree to bf16 rounding of the sum
+            ref = ffn.FfnBlock(a.tokens, a.hidden, a.inner // world, w1r, s1r, w2r, s2, torch).run(X).float()
+            got = blk.run(X).float()
+            torch.cuda.synchronize()
+            err = float((got - ref).abs().max() / ref.abs().max())
+            print(f"rank {rank}: peer exchange vs NCCL all-reduce: max |diff| / max |ref| = {err:.3e}", flush=True)
+            assert err < 2e-2, err
     elif a.op == "attention":
         shape = (a.batch_heads, a.seq, a.d)
         Q, K_, V = _dev(dt, shape, 7, 1.0), _dev(dt, shape, 8, 1.0), _dev(dt, shape, 9, 1.0); O = torch.zeros_like(Q)
@@ -130,6 +139,8 @@ def main():
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms = float(t[0])
         torch.distributed.barrier()
+        if a.op == "ffn" and getattr(blk, "peer", None) is not None:
+            blk.peer.close()
         torch.distributed.destroy_process_group()
         if rank != 0:
             return

@@ -101,3 +101,46 @@ def test_ffn_workspace_is_checked(backend):
     with pytest.raises(backend.BackendError, match="workspace"):
         backend.ffn_block(256, 256, 1024, x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), 1024)
     assert backend.ffn_workspace_bytes(8192, 4096, 16384) > 8192 * 16384 * 3
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ffn_peer_exchange_emulated_on_one_gpu(backend, oracle_lib, world):
+    # The tensor-parallel block without a library collective, all ranks played in turn by this process on one GPU (the
+    # kernels never wait on one another, so that is legitimate): every rank's second GEMM scatters its partial rows into the
+    # owners' receive buffers, then every rank reduces what it received and stores its rows into every rank's output.
+    # Bit-exact against the fp32 sum of the per-rank partials of the ordinary block, and within the fp8 tolerance of the oracle.
+    import torch
+    from pyc_b200 import ffn
+    from gpu_util import rel_err, sync_ok
+    T, H, I = 512, 1024, 4096
+    xb, w1, s1, w2, s2 = workloads.ffn_inputs(T, H, I)
+    X = torch.from_numpy(xb.view(np.int16)).cuda()
+    rows = T // world
+    recv = [torch.zeros((world, rows, H), dtype=torch.int16, device="cuda") for _ in range(world)]
+    outs = [torch.zeros((T, H), dtype=torch.int16, device="cuda") for _ in range(world)]
+    partial_sum = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    keep = []
+    for r in range(world):
+        w1r, s1r, w2r = ffn.shard_weights(w1, s1, w2, r, world)
+        d = [torch.from_numpy(np.ascontiguousarray(t)).cuda() for t in (w1r, s1r.astype(np.float32), w2r, s2.astype(np.float32))]
+        keep.append(d)
+        ws_bytes = backend.ffn_workspace_bytes(T, H, I // world)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+        backend.ffn_block_scatter(T, H, I // world, X.data_ptr(), d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[3].data_ptr(),
+                                  ws.data_ptr(), ws_bytes, [t.data_ptr() for t in recv], r)
+        part = torch.zeros((T, H), dtype=torch.int16, device="cuda")
+        backend.ffn_block(T, H, I // world, X.data_ptr(), d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[3].data_ptr(),
+                          part.data_ptr(), ws.data_ptr(), ws_bytes)
+        partial_sum += part.view(torch.bfloat16).float()      # same order as the reduction kernel: rank 0, 1, ...
+        # the scatter put exactly this rank's partial rows into slot r of each owner
+        for o in range(world):
+            assert torch.equal(recv[o][r], part[o * rows:(o + 1) * rows])
+    for r in range(world):
+        backend.tp_reduce_broadcast(recv[r].data_ptr(), [t.data_ptr() for t in outs], r, rows, H)
+    sync_ok()
+    want_bits = partial_sum.to(torch.bfloat16).view(torch.int16)
+    for o in outs:
+        assert torch.equal(o, want_bits)
+    ref = oracle.ffn_reference(oracle_lib, workloads.bf16_bits_to_f32(xb), w1, s1, w2, s2)
+    got = workloads.bf16_bits_to_f32(outs[0].cpu().numpy().view(np.uint16))
+    assert rel_err(got, ref) <= 6e-2
