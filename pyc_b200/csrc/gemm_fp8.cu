@@ -26,6 +26,7 @@ constexpr int BM = 128;
 constexpr int BK = 128;                      // fp8 elements per stage row = 128 bytes
 constexpr int A_STAGE_BYTES = BM * BK;
 constexpr int GROUP_M = 16;
+constexpr int EPI_STAGE_BYTES = 4 * 32 * 128;   // epilogue staging: 32 rows x 128 bytes per warp
 
 struct Fp8Epilogue {
     __nv_bfloat16* D;
@@ -52,14 +53,27 @@ __device__ __forceinline__ void fp8_tile_coords(int tile, int tiles_m, int tiles
 
 // Epilogue of one accumulator tile for one thread (= one row): BN columns from TMEM at `acc_addr`, dequantise, bias,
 // activation, bf16 out.  Shared by the single-CTA and the CTA-pair kernel.
-template <int BN>
-__device__ __forceinline__ void fp8_epilogue_tile(const Fp8Epilogue& ep, uint32_t acc_addr, int row, int n0, int M, int N, bool vec_ok) {
-    const float rs = (ep.row_scale && row < M) ? ep.row_scale[row] : 1.0f;
-    __nv_bfloat16* drow = ep.D + static_cast<size_t>(row) * N;
-    if (ep.world > 0 && row < M) {
+// Where row `row` of the result starts: in D, or (tensor parallel) in the owning rank's receive slot for this rank.
+__device__ __forceinline__ __nv_bfloat16* fp8_out_row(const Fp8Epilogue& ep, int row, int N) {
+    if (ep.world > 0) {
         const int owner = row / ep.rows_per_rank;
-        drow = ep.dst[owner] + (static_cast<size_t>(ep.src_rank) * ep.rows_per_rank + (row - owner * ep.rows_per_rank)) * N;
+        return ep.dst[owner] + (static_cast<size_t>(ep.src_rank) * ep.rows_per_rank + (row - owner * ep.rows_per_rank)) * N;
     }
+    return ep.D + static_cast<size_t>(row) * N;
+}
+
+// `stage`: 4 KB of shared memory private to the calling warp (32 rows x 128 bytes).  With vec_ok the results of 64
+// columns are parked there, one row per lane, and written out with every store instruction covering four whole
+// 128-byte row segments: full lines instead of 32 scattered 16-byte pieces, which matters most when the rows go to
+// another GPU over NVLink.  16-byte chunk c of row r sits at chunk position c ^ (r & 7), so neither side conflicts.
+template <int BN>
+__device__ __forceinline__ void fp8_epilogue_tile(const Fp8Epilogue& ep, uint32_t acc_addr, int row, int n0, int M, int N, bool vec_ok,
+                                                  uint8_t* stage) {
+    const int lane = threadIdx.x & 31;
+    const int row0 = row - lane;   // first row of this warp
+    const float rs = (ep.row_scale && row < M) ? ep.row_scale[row] : 1.0f;
+    __nv_bfloat16* drow = row < M ? fp8_out_row(ep, row, N) : ep.D;
+    bool use_stage = false;
     // One 32-column chunk; the next chunk's TMEM load is already in flight while this one is computed.
     auto chunk = [&](const uint32_t (&r)[32], int c) {
         const int col0 = n0 + c * 32;  // warp-uniform
@@ -114,7 +128,12 @@ __device__ __forceinline__ void fp8_epilogue_tile(const Fp8Epilogue& ep, uint32_
                     uint4 u;
                     u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
                     u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
-                    dst[q] = u;
+                    if (use_stage) {   // chunk (c & 1) * 4 + q of this lane's row
+                        const int cc = ((c & 1) * 4 + q) ^ (lane & 7);
+                        *reinterpret_cast<uint4*>(stage + lane * 128 + cc * 16) = u;
+                    } else {
+                        dst[q] = u;
+                    }
                 }
             } else {
                 for (int j = 0; j < 32; ++j) if (col0 + j < N) drow[col0 + j] = __float2bfloat16_rn(v[j]);
@@ -125,6 +144,7 @@ __device__ __forceinline__ void fp8_epilogue_tile(const Fp8Epilogue& ep, uint32_
     tmem_ld_32x32(acc_addr, r0);
 #pragma unroll 1
     for (int c = 0; c < BN / 32; c += 2) {
+        use_stage = stage != nullptr && vec_ok && n0 + c * 32 + 64 <= N;   // warp-uniform: all 64 columns exist
         tmem_ld_wait();
         tmem_ld_32x32(acc_addr + (c + 1) * 32, r1);
         chunk(r0, c);
@@ -133,6 +153,20 @@ __device__ __forceinline__ void fp8_epilogue_tile(const Fp8Epilogue& ep, uint32_
         if (c + 2 < BN / 32) tmem_ld_32x32(acc_addr + (c + 2) * 32, r0);
         chunk(r1, c + 1);
         __syncwarp();
+        if (use_stage) {
+            // 64 columns of 32 rows are parked: store instruction i covers rows 4i .. 4i+3, eight lanes per row
+            const int colv = n0 + c * 32 + (lane & 7) * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int rr = 4 * i + (lane >> 3);
+                const int grow = row0 + rr;
+                if (grow < M && colv + 8 <= N) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(stage + rr * 128 + (((lane & 7) ^ (rr & 7)) * 16));
+                    *reinterpret_cast<uint4*>(fp8_out_row(ep, grow, N) + colv) = u;
+                }
+            }
+            __syncwarp();
+        }
     }
 }
 
@@ -148,7 +182,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_STAGE_BYTES);
+    uint8_t* sOut = sB + STAGES * B_STAGE_BYTES;                     // 4 epilogue warps x 4 KB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + EPI_STAGE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
 
@@ -240,7 +275,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int n0 = tn * BN;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase, status, 0x34)) break;
             tc_fence_after();
-            fp8_epilogue_tile<BN>(ep, tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * BN, row, n0, M, N, vec_ok);
+            fp8_epilogue_tile<BN>(ep, tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * BN, row, n0, M, N, vec_ok, sOut + wq * 4096);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
@@ -259,7 +294,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 template <int BN, int STAGES, bool B_KMAJOR>
 int launch_fp8_instance(int M, int N, int K, const void* A, const void* B, const Fp8Epilogue& ep, cudaStream_t stream, int* status) {
     auto kernel = gemm_fp8_kernel<BN, STAGES, B_KMAJOR>;
-    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + BN * BK) + (2 * STAGES + 4) * 8 + 16;
+    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + BN * BK) + EPI_STAGE_BYTES + (2 * STAGES + 4) * 8 + 16;
     static bool attr_set[16] = {};
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
@@ -282,7 +317,7 @@ int launch_fp8_instance(int M, int N, int K, const void* A, const void* B, const
 // ---------------------------------------------------------------------------------------
 // CTA-pair form (cta_group::2, 256 x 256 x 32 per instruction), the fp8 twin of the bf16 pair
 // kernel: a pair owns a 256 x 256 tile, each CTA loads its 128 A rows and HALF of the B tile
-// (32 KB per stage instead of 48 KB, ring 7 deep), the leader's single thread issues for both
+// (32 KB per stage instead of 48 KB, ring 6 deep plus 16 KB of epilogue staging), the leader's single thread issues for both
 // tensor cores, loads of both CTAs count on the leader's "full" barrier, epilogue warps of both
 // CTAs release the accumulator on the leader's barrier.  No multicast of any kind.
 // ---------------------------------------------------------------------------------------
@@ -311,7 +346,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * PB_STAGE_BYTES);
+    uint8_t* sOut = sB + STAGES * PB_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + EPI_STAGE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
 
@@ -407,7 +443,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             const int n0 = tn * PBN;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase, status, 0x38)) break;
             tc_fence_after();
-            fp8_epilogue_tile<PBN>(ep, tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * PBN, row, n0, M, N, vec_ok);
+            fp8_epilogue_tile<PBN>(ep, tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * PBN, row, n0, M, N, vec_ok, sOut + wq * 4096);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * acc);
@@ -428,7 +464,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 template <int STAGES, bool B_KMAJOR>
 int launch_fp8_pair_instance(int M, int N, int K, const void* A, const void* B, const Fp8Epilogue& ep, cudaStream_t stream, int* status) {
     auto kernel = gemm_fp8_pair_kernel<STAGES, B_KMAJOR>;
-    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + PB_STAGE_BYTES) + (2 * STAGES + 4) * 8 + 16;
+    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + PB_STAGE_BYTES) + EPI_STAGE_BYTES + (2 * STAGES + 4) * 8 + 16;
     static bool attr_set[16] = {};
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
@@ -479,7 +515,7 @@ int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col
     const char* pe = getenv("PYC_B200_FP8_PAIR");
     const long long pair_tiles = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
     if (pe && (pe[0] == '0' || pe[0] == '1') ? pe[0] == '1' : pair_tiles >= sms / 2)
-        return b_col_major ? launch_fp8_pair_instance<7, true>(M, N, K, A, B, ep, stream, status) : launch_fp8_pair_instance<7, false>(M, N, K, A, B, ep, stream, status);
+        return b_col_major ? launch_fp8_pair_instance<6, true>(M, N, K, A, B, ep, stream, status) : launch_fp8_pair_instance<6, false>(M, N, K, A, B, ep, stream, status);
     if (use256) return b_col_major ? launch_fp8_instance<256, 4, true>(M, N, K, A, B, ep, stream, status) : launch_fp8_instance<256, 4, false>(M, N, K, A, B, ep, stream, status);
     return b_col_major ? launch_fp8_instance<128, 6, true>(M, N, K, A, B, ep, stream, status) : launch_fp8_instance<128, 6, false>(M, N, K, A, B, ep, stream, status);
 }
