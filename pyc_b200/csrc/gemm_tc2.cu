@@ -29,6 +29,7 @@ constexpr int BK = 64;
 constexpr int A_STAGE = BM * BK * 2;    // 16 KB
 constexpr int B_STAGE = BNH * BK * 2;   // 16 KB
 constexpr int GROUP_M = 8;              // in pair tiles (8 x 256 rows)
+constexpr int EPI_STAGE_BYTES = 4 * 32 * 128;   // epilogue staging (6-stage form): 32 rows x 128 bytes per warp
 
 struct Epi2 {
     void* D;
@@ -76,8 +77,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;
+    // With 7 ring stages there is no room left; with 6, each epilogue warp gets 4 KB to park 64 columns of its 32 rows
+    // and write them out as whole 128-byte row segments instead of 32 scattered pieces per store instruction.
+    constexpr bool STAGED = STAGES <= 6;
     uint8_t* sB = smem + STAGES * A_STAGE;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_STAGE);
+    uint8_t* sOut = sB + STAGES * B_STAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + (STAGED ? EPI_STAGE_BYTES : 0));
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
 
@@ -201,6 +206,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tc_fence_after();
             T* drow = reinterpret_cast<T*>(ep.D) + static_cast<size_t>(row) * N;
             const uint32_t acc_addr = lane_base + acc * BN;
+            uint8_t* stage = sOut + wq * 4096;
+            const int row0 = row - lane;   // first row of this warp
+            bool use_stage = false;
             // One 32-column chunk: scale, add, activation, 64 bytes out.  The next chunk's TMEM load is already in flight.
             auto chunk = [&](const uint32_t (&r)[32], int c) {
                 const int col0 = n0 + c * 32;  // warp-uniform
@@ -237,7 +245,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     uint32_t w[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) w[j] = E::pack(v[2 * j], v[2 * j + 1]);
-                    if (ep.vec_ok == 2) {
+                    if (STAGED && use_stage) {   // 16-byte chunk (c & 1) * 4 + q of this lane's row, at position chunk ^ (row & 7)
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            *reinterpret_cast<uint4*>(stage + lane * 128 + ((((c & 1) * 4 + q) ^ (lane & 7)) * 16)) =
+                                make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                    } else if (ep.vec_ok == 2) {
                         const uint32_t lo[8] = {w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]};
                         const uint32_t hi[8] = {w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]};
                         st_global_v8(drow + col0, lo);
@@ -255,6 +268,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tmem_ld_32x32(acc_addr, r0);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c += 2) {
+                use_stage = STAGED && ep.vec_ok && n0 + c * 32 + 64 <= N;   // warp-uniform: all 64 columns exist
                 tmem_ld_wait();
                 tmem_ld_32x32(acc_addr + (c + 1) * 32, r1);
                 chunk(r0, c);
@@ -263,6 +277,19 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (c + 2 < BN / 32) tmem_ld_32x32(acc_addr + (c + 2) * 32, r0);
                 chunk(r1, c + 1);
                 __syncwarp();
+                if (STAGED && use_stage) {
+                    // store instruction i covers rows 4i .. 4i+3 of the warp, eight lanes (8 x 16 bytes) per row
+                    const int colv = n0 + c * 32 + (lane & 7) * 8;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = 4 * i + (lane >> 3);
+                        if (row0 + rr < M) {
+                            const uint4 u = *reinterpret_cast<const uint4*>(stage + rr * 128 + (((lane & 7) ^ (rr & 7)) * 16));
+                            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(ep.D) + static_cast<size_t>(row0 + rr) * N + colv) = u;
+                        }
+                    }
+                    __syncwarp();
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -284,7 +311,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 template <int STAGES, bool B_KMAJOR, int FMT>
 int launch_pair_instance(const GemmProblem& p, cudaStream_t stream, int* status) {
     auto kernel = gemm_tc2_kernel<STAGES, B_KMAJOR, FMT>;
-    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE + B_STAGE) + (2 * STAGES + 4) * 8 + 16;
+    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE + B_STAGE) + (STAGES <= 6 ? EPI_STAGE_BYTES : 0) + (2 * STAGES + 4) * 8 + 16;
     static bool attr_set[16] = {};
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
@@ -316,8 +343,11 @@ int launch_pair_instance(const GemmProblem& p, cudaStream_t stream, int* status)
 }  // namespace
 
 int launch_gemm_tc_pair(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream, int* status) {
-    (void)cfg;
     const bool bf16 = p.dtype == PYC_DTYPE_BF16;
+    if (cfg.stages == 6) {   // six ring stages + staged epilogue stores
+        if (p.b_col_major) return bf16 ? launch_pair_instance<6, true, 1>(p, stream, status) : launch_pair_instance<6, true, 0>(p, stream, status);
+        return bf16 ? launch_pair_instance<6, false, 1>(p, stream, status) : launch_pair_instance<6, false, 0>(p, stream, status);
+    }
     if (p.b_col_major) return bf16 ? launch_pair_instance<7, true, 1>(p, stream, status) : launch_pair_instance<7, true, 0>(p, stream, status);
     return bf16 ? launch_pair_instance<7, false, 1>(p, stream, status) : launch_pair_instance<7, false, 0>(p, stream, status);
 }

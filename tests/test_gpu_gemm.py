@@ -10,7 +10,7 @@ from pyc_b200 import abi, workloads
 
 pytestmark = pytest.mark.gpu
 
-TC = ["tc_128x256x64_s4", "tc_128x128x64_s6", "tc_128x64x64_s8", "tc2_256x256x64_s7"]
+TC = ["tc_128x256x64_s4", "tc_128x128x64_s6", "tc_128x64x64_s8", "tc2_256x256x64_s7", "tc2_256x256x64_s6"]
 SIMT = ["simt_128x128x16", "simt_64x64x16", "simt_32x64x16"]
 NAME = {abi.DTYPE_F32: "f32", abi.DTYPE_BF16: "bf16", abi.DTYPE_F16: "f16"}
 
