@@ -324,6 +324,8 @@ int launch_fp8_instance(int M, int N, int K, const void* A, const void* B, const
 constexpr int PBN = 256, PBNH = 128;
 constexpr int PB_STAGE_BYTES = PBNH * BK;     // 16 KB
 constexpr int P_GROUP_M = 8;                  // in pair tiles (8 x 256 rows)
+constexpr int PAIR_EPI_WARPS = 8;
+constexpr int PAIR_THREADS = 64 + 32 * PAIR_EPI_WARPS;
 
 __device__ __forceinline__ void fp8_pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
     const int group = P_GROUP_M * tiles_n;
@@ -336,7 +338,7 @@ __device__ __forceinline__ void fp8_pair_tile_coords(int tile, int tiles_m, int 
 }
 
 template <int STAGES, bool B_KMAJOR>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Fp8Epilogue ep, int M, int N, int K, int* status) {
     constexpr uint32_t PAIR_TX = 2 * (A_STAGE_BYTES + PB_STAGE_BYTES);
     constexpr uint32_t TMEM_COLS = 2 * PBN;
@@ -347,7 +349,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
     uint8_t* sOut = sB + STAGES * PB_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + EPI_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + PAIR_EPI_WARPS * 4096);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
 
@@ -362,7 +364,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 8); }  // 4 epilogue warps x 2 CTAs
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 2 * PAIR_EPI_WARPS); }  // epilogue warps of both CTAs
         fence_barrier_init();
         fence_proxy_async();
     }
@@ -430,7 +432,11 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             }
         }
     } else {
+        // Eight epilogue warps: two per TMEM lane quarter, each taking half of the tile's columns.  With fp8 the main loop of a
+        // tile is half as long as with bf16 while the epilogue (dequantise, bias, GELU, pack) is the same work, so four warps
+        // could not keep up at K = 4096.
         const int wq = warp & 3;
+        const int half = (warp - 2) >> 2;
         const uint32_t tempty_leader0 = map_to_cta(tempty0, 0);
         const bool vec_ok = (N % 8 == 0) && (reinterpret_cast<uintptr_t>(ep.D) % 16 == 0) &&
                             (reinterpret_cast<uintptr_t>(ep.col_scale) % 16 == 0) && (reinterpret_cast<uintptr_t>(ep.bias) % 16 == 0);
@@ -443,7 +449,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             const int n0 = tn * PBN;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase, status, 0x38)) break;
             tc_fence_after();
-            fp8_epilogue_tile<PBN>(ep, tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * PBN, row, n0, M, N, vec_ok, sOut + wq * 4096);
+            fp8_epilogue_tile<PBN / 2>(ep, tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + acc * PBN + half * (PBN / 2), row, n0 + half * (PBN / 2), M, N,
+                                       vec_ok, sOut + (warp - 2) * 4096);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * acc);
@@ -464,7 +471,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 template <int STAGES, bool B_KMAJOR>
 int launch_fp8_pair_instance(int M, int N, int K, const void* A, const void* B, const Fp8Epilogue& ep, cudaStream_t stream, int* status) {
     auto kernel = gemm_fp8_pair_kernel<STAGES, B_KMAJOR>;
-    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + PB_STAGE_BYTES) + EPI_STAGE_BYTES + (2 * STAGES + 4) * 8 + 16;
+    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + PB_STAGE_BYTES) + PAIR_EPI_WARPS * 4096 + (2 * STAGES + 4) * 8 + 16;
     static bool attr_set[16] = {};
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
@@ -479,7 +486,7 @@ int launch_fp8_pair_instance(int M, int N, int K, const void* A, const void* B, 
     const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + PBN - 1) / PBN);
     const int max_pairs = sm_count() / 2;
     const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
-    kernel<<<grid, 192, smem, stream>>>(tmA, tmB, ep, M, N, K, status);
+    kernel<<<grid, PAIR_THREADS, smem, stream>>>(tmA, tmB, ep, M, N, K, status);
     B200_CUDA_OK(cudaGetLastError());
     count_launch();
     return 0;
