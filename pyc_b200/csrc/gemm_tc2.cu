@@ -66,7 +66,7 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
 }
 
 template <int STAGES, bool B_KMAJOR, int FMT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STAGES <= 6 ? 320 : 192, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi2 ep, int M, int N, int K, int* status) {
     constexpr uint32_t PAIR_TX = 2 * (A_STAGE + B_STAGE);  // bytes both CTAs deliver per stage
     constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -80,9 +80,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // With 7 ring stages there is no room left; with 6, each epilogue warp gets 4 KB to park 64 columns of its 32 rows
     // and write them out as whole 128-byte row segments instead of 32 scattered pieces per store instruction.
     constexpr bool STAGED = STAGES <= 6;
+    // The 6-stage form also runs eight epilogue warps (two per TMEM lane quarter, half of the tile's columns each): the epilogue's
+    // stay beside the next tile's main loop is half as long.
+    constexpr int EPI_WARPS = STAGED ? 8 : 4;
     uint8_t* sB = smem + STAGES * A_STAGE;
     uint8_t* sOut = sB + STAGES * B_STAGE;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + (STAGED ? EPI_STAGE_BYTES : 0));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + (STAGED ? EPI_WARPS * 4096 : 0));
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
 
@@ -97,7 +100,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 8); }  // 4 epilogue warps x 2 CTAs
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 2 * EPI_WARPS); }  // epilogue warps of both CTAs
         fence_barrier_init();
         fence_proxy_async();
     }
@@ -191,6 +194,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     } else {
         const int wq = warp & 3;
+        constexpr int CHUNKS_PER_WARP = (BN / 32) / (EPI_WARPS / 4);
+        const int c_begin = ((warp - 2) >> 2) * CHUNKS_PER_WARP, c_end = c_begin + CHUNKS_PER_WARP;
         const uint32_t tempty_leader0 = map_to_cta(tempty0, 0);
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(wq * 32) << 16);
         const T* addp = reinterpret_cast<const T*>(ep.add);
@@ -206,7 +211,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tc_fence_after();
             T* drow = reinterpret_cast<T*>(ep.D) + static_cast<size_t>(row) * N;
             const uint32_t acc_addr = lane_base + acc * BN;
-            uint8_t* stage = sOut + wq * 4096;
+            uint8_t* stage = sOut + (warp - 2) * 4096;
             const int row0 = row - lane;   // first row of this warp
             bool use_stage = false;
             // One 32-column chunk: scale, add, activation, 64 bytes out.  The next chunk's TMEM load is already in flight.
@@ -265,16 +270,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             };
             uint32_t r0[32], r1[32];
-            tmem_ld_32x32(acc_addr, r0);
+            tmem_ld_32x32(acc_addr + c_begin * 32, r0);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c += 2) {
+            for (int c = c_begin; c < c_end; c += 2) {
                 use_stage = STAGED && ep.vec_ok && n0 + c * 32 + 64 <= N;   // warp-uniform: all 64 columns exist
                 tmem_ld_wait();
                 tmem_ld_32x32(acc_addr + (c + 1) * 32, r1);
                 chunk(r0, c);
                 __syncwarp();
                 tmem_ld_wait();
-                if (c + 2 < BN / 32) tmem_ld_32x32(acc_addr + (c + 2) * 32, r0);
+                if (c + 2 < c_end) tmem_ld_32x32(acc_addr + (c + 2) * 32, r0);
                 chunk(r1, c + 1);
                 __syncwarp();
                 if (STAGED && use_stage) {
@@ -311,7 +316,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 template <int STAGES, bool B_KMAJOR, int FMT>
 int launch_pair_instance(const GemmProblem& p, cudaStream_t stream, int* status) {
     auto kernel = gemm_tc2_kernel<STAGES, B_KMAJOR, FMT>;
-    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE + B_STAGE) + (STAGES <= 6 ? EPI_STAGE_BYTES : 0) + (2 * STAGES + 4) * 8 + 16;
+    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE + B_STAGE) + (STAGES <= 6 ? 8 * 4096 : 0) + (2 * STAGES + 4) * 8 + 16;
     static bool attr_set[16] = {};
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
@@ -334,7 +339,7 @@ int launch_pair_instance(const GemmProblem& p, cudaStream_t stream, int* status)
     const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
     const int max_pairs = sm_count() / 2;
     const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
-    kernel<<<grid, 192, smem, stream>>>(tmA, tmB, ep, p.M, p.N, p.K, status);
+    kernel<<<grid, STAGES <= 6 ? 320 : 192, smem, stream>>>(tmA, tmB, ep, p.M, p.N, p.K, status);
     B200_CUDA_OK(cudaGetLastError());
     count_launch();
     return 0;

@@ -208,7 +208,7 @@ static RegState& reg_state() { static RegState* s = new RegState(); return *s; }
 
 static const GemmConfig kGemmConfigs[] = {
     // symbol suffix           kind       dtypes (bf16|f16 = 8|4, f32 = 2)  bm   bn   bk  st  prio  smem    workload
-    {"tc2_256x256x64_s6", GEMM_TC_PAIR, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 256, 256, 64, 6, 96, 214160, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
+    {"tc2_256x256x64_s6", GEMM_TC_PAIR, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 256, 256, 64, 6, 96, 230576, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
     {"tc2_256x256x64_s7", GEMM_TC_PAIR, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 256, 256, 64, 7, 95, 230560, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
     {"tc_128x256x64_s4", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 256, 64, 4, 100, 197744, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
     {"tc_128x128x64_s6", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 128, 64, 6, 90, 197776, PYC_KERNEL_WORKLOAD_SQUARE},
