@@ -31,6 +31,26 @@ __device__ __forceinline__ float q_block_reduce(float v, float* scratch, bool is
     return v;
 }
 
+// Sum, sum of squares, minimum and maximum over the block in ONE exchange (two barriers).
+__device__ __forceinline__ void q_block_reduce_stats(float& s, float& ss, float& mn, float& mx, float (*scratch4)[4]) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s += __shfl_xor_sync(0xffffffffu, s, o); ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o)); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();
+    if (l == 0) { scratch4[w][0] = s; scratch4[w][1] = ss; scratch4[w][2] = mn; scratch4[w][3] = mx; }
+    __syncthreads();
+    const bool in = l < QT / 32;
+    s = in ? scratch4[l][0] : 0.0f; ss = in ? scratch4[l][1] : 0.0f; mn = in ? scratch4[l][2] : INFINITY; mx = in ? scratch4[l][3] : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s += __shfl_xor_sync(0xffffffffu, s, o); ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o)); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+}
+
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -45,7 +65,7 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 
 // VPT vectors of 8 bf16 per thread cached (cols <= QT*8*VPT); cols % 8 == 0.
 template <int VPT, bool LN>
-__global__ void __launch_bounds__(QT, 4)
+__global__ void __launch_bounds__(QT, VPT <= 2 ? 6 : 4)   // narrow rows: more rows in flight per SM
 rowquant_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
                 uint8_t* __restrict__ q, float* __restrict__ scale, size_t rows, size_t cols, float eps) {
     __shared__ float scratch[8];
@@ -60,6 +80,43 @@ rowquant_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
         }
         float mean = 0.0f, rstd = 1.0f;
         if constexpr (LN) {
+            if (!gamma && !beta) {
+                // Plain normalisation: (x - mean) * rstd is monotonic in x, so the row's largest |y| follows from its minimum
+                // and maximum, and mean, variance, min and max come out of one block exchange.  Sums are taken about the row's
+                // first element so that a large common offset does not cancel in E[x^2] - E[x]^2.
+                __shared__ float scratch4[QT / 32][4];
+                const float pivot = __bfloat162float(xr[0]);
+                float s = 0.0f, ss = 0.0f, mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+                    if (threadIdx.x + static_cast<size_t>(i) * QT < nvec) {
+                        float f[8]; unpack8(raw[i], f);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) { const float d = f[j] - pivot; s += d; ss = fmaf(d, d, ss); mn = fminf(mn, f[j]); mx = fmaxf(mx, f[j]); }
+                    }
+                q_block_reduce_stats(s, ss, mn, mx, scratch4);
+                const float n_inv = 1.0f / static_cast<float>(cols);
+                const float ds = s * n_inv;
+                mean = pivot + ds;
+                rstd = rsqrtf(fmaxf(ss * n_inv - ds * ds, 0.0f) + eps);
+                const float amax_y = fmaxf(fabsf(mx - mean), fabsf(mn - mean)) * rstd;
+                const float sc_y = amax_y > 0.0f ? amax_y * (1.0f / 448.0f) : 1.0f;
+                if (threadIdx.x == 0) scale[row] = sc_y;
+                const float a = rstd / sc_y, b = -mean * a;     // quantised value = x * a + b
+                uint2* qr = reinterpret_cast<uint2*>(q + row * cols);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const size_t vi = threadIdx.x + static_cast<size_t>(i) * QT;
+                    if (vi < nvec) {
+                        float f[8]; unpack8(raw[i], f);
+                        uint2 o;
+                        o.x = pack_e4m3x4(fmaf(f[0], a, b), fmaf(f[1], a, b), fmaf(f[2], a, b), fmaf(f[3], a, b));
+                        o.y = pack_e4m3x4(fmaf(f[4], a, b), fmaf(f[5], a, b), fmaf(f[6], a, b), fmaf(f[7], a, b));
+                        qr[vi] = o;
+                    }
+                }
+                continue;
+            }
             float s = 0.0f;
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
@@ -122,7 +179,7 @@ int launch_rowquant(const void* x, const void* gamma, const void* beta, void* q,
     if (!al(x) || !al(gamma) || !al(beta) || reinterpret_cast<uintptr_t>(q) % 8) { set_error("row quantise: pointers must be 16-byte aligned"); return -1; }
     const size_t nvec = cols / 8;
     size_t grid = rows;
-    const size_t cap = static_cast<size_t>(sm_count()) * 32;
+    const size_t cap = static_cast<size_t>(sm_count()) * 64;
     if (grid > cap) grid = cap;
     const auto* xb = static_cast<const __nv_bfloat16*>(x); const auto* g = static_cast<const __nv_bfloat16*>(gamma); const auto* b = static_cast<const __nv_bfloat16*>(beta);
     auto* qq = static_cast<uint8_t*>(q);
