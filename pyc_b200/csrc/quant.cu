@@ -65,7 +65,7 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 
 // VPT vectors of 8 bf16 per thread cached (cols <= QT*8*VPT); cols % 8 == 0.
 template <int VPT, bool LN>
-__global__ void __launch_bounds__(QT, VPT <= 2 ? 5 : 4)   // narrow rows: more rows in flight per SM
+__global__ void __launch_bounds__(QT, 4)
 rowquant_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
                 uint8_t* __restrict__ q, float* __restrict__ scale, size_t rows, size_t cols, float eps) {
     __shared__ float scratch[8];
