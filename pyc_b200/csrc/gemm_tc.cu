@@ -49,12 +49,6 @@ struct Epilogue {
     int l2_hints;    // 0 none, 1 A evict_last + B evict_first, 2 both evict_last
 };
 
-__device__ __forceinline__ float apply_act(float v, int act) {
-    if (act == PYC_B200_ACT_RELU) return v > 0.0f ? v : 0.0f;
-    if (act == PYC_B200_ACT_GELU) return gelu_erf(v);
-    return v;
-}
-
 template <int FMT> struct Elem;
 template <> struct Elem<1> {
     using T = __nv_bfloat16;
