@@ -150,6 +150,18 @@ int pyc_b200_gemm(const pyc_b200_gemm_args* args, void* stream);
  * ignored (the tile width is chosen from the shape). */
 int pyc_b200_gemm_static(const pyc_b200_gemm_args* args, void* stream);
 
+/* No counterpart in PyC.  Status of the static entry point's kernels, also without
+ * any allocation: enqueues one 4-byte copy of the shared block's status word into
+ * *host_out on `stream` (use pinned memory for a truly asynchronous copy) and
+ * returns; after the caller has synchronised that stream, *host_out is 0 when every
+ * wait of the preceding pyc_b200_gemm_static kernels completed, otherwise
+ * (site << 8) | 1 for the first wait that ran out -- the output of that GEMM is then
+ * not valid.  The word is cleared by the next pyc_b200_gemm_static call, so read it
+ * before issuing another one.  pyc_b200_device_status() does NOT see this word (it
+ * reads the per-device context that the allocating entry points create).  Before
+ * the first static call on a device *host_out is set to 0 directly. */
+int pyc_b200_gemm_static_status(int* host_out, void* stream);
+
 /* Elementwise / reduction ops on device pointers (HBM-bound kernels). */
 int pyc_b200_add(pyc_dtype dtype, const void* a, const void* b, void* out, size_t elems, void* stream);
 int pyc_b200_bias_act(pyc_dtype dtype, const void* x, const void* add, pyc_b200_add_mode add_mode,
@@ -205,6 +217,19 @@ typedef struct {
 size_t pyc_b200_ffn_workspace_bytes(int tokens, int hidden, int inner);
 int pyc_b200_ffn_block(const pyc_b200_ffn_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Tensor-parallel FFN through PyC's collective interface.  Each rank calls this with its shard (as described above:
+ * column slice of W1 / b1 / w1_scale, row slice of W2, b2 on one rank) and the vtable of a loaded collective backend
+ * (pyc_collective_comm, include/pyc/collective_comm.h:30-101; PyC's loader is pyc_load_comm_backend,
+ * src/compiler/runtime/comm_backend_loader.c) plus the communicator handle its launcher created (PyC hands it around as
+ * "comm_handle", src/compiler/runtime/distributed_runtime.c:16-42).  The block runs, then ONE all_reduce (sum) of the
+ * [tokens, hidden] partial sums is issued through comm->all_reduce with PYC_DTYPE_BF16, in place on args->out, on `stream`.
+ * PyC's own NCCL shim has no bf16 mapping (src/compiler/runtime/comm_backend_nccl.c:139-150 knows I8/I32/F16/F32);
+ * libpyc_b200_comm_nccl.so in this package is a backend for the same interface that has it.  world == 1 needs no vtable.
+ * Returns 0, or -1 (message in pyc_b200_last_error()) for bad arguments or a collective status other than PYC_COMM_OK.
+ * PyC's own pyc_run_model never calls a collective (its options only carry world_size / rank). */
+int pyc_b200_ffn_block_tp(const pyc_b200_ffn_args* args, const pyc_collective_comm* comm, pyc_comm_handle_t comm_handle,
+                          int world, int rank, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Tensor-parallel FFN without a library collective: the reduce-scatter is done by the second GEMM's epilogue and the
  * all-gather by the reduction kernel, both with plain stores into peer memory over NVLink.
  *   - every rank owns tokens / world consecutive rows of the result and a receive buffer [world][tokens/world][hidden]
@@ -237,6 +262,36 @@ int pyc_b200_symm_free(void* ptr);
  * Returns the number of configurations timed, or -1. */
 int pyc_b200_autotune_gemm(pyc_dtype dtype, int M, int N, int K, int iters,
                            char* best_symbol, size_t best_symbol_size, double* best_ms);
+
+/* Persisted autotune results, in the line format of PyC's autotune DB ("op|backend|symbol|best_ms",
+ * src/compiler/compiler_api.c:2145-2305, path rule :2124-2143: PYC_AUTOTUNE_DB_PATH).  pyc_b200_autotune_gemm and the
+ * PYC_B200_AUTOTUNE=1 dispatch path append every timing under flock("<path>.lock") and compact the file as PyC does.
+ * Lines with op "matmul" are the per-symbol timings PyC's own loader reads; lines with op "matmul@<dtype>:<M>x<N>x<K>"
+ * carry the same timings per shape, and the fastest symbol of a shape becomes that shape's choice in the next process.
+ * The DB is read once when the library registers its kernels; this call reads `path` (NULL: PYC_AUTOTUNE_DB_PATH) again.
+ * Returns the number of per-shape winners installed, 0 when the file does not exist, -1 without a path. */
+int pyc_b200_autotune_db_load(const char* path);
+
+/* The plan of the most recent GPU run of `module` in this process (NULL: of the most recent run of any module): one text
+ * line per step, "step <i>: <kernel symbol> [<who chose it>] <- <op>#<id> + <op>#<id> ...", naming the IR ops each kernel
+ * absorbed.  PyC's own fusion pass renames ops and drops the epilogue (src/compiler/passes/pass_manager.c:241-267) and its
+ * "matmul_fused" catalog holds placeholders (src/compiler/compiler_api.c:2094-2122), so
+ * pyc_run_stats.selected_kernel_symbol cannot name the kernel that ran; this does, without touching a PyC header.
+ * "who chose it" is autotune | env | promoted | registry | model (see pyc_cuda_dispatch's selection order in runtime.cu).
+ * Returns the length of the full text (copy truncated to out_size - 1), or -1 if that module has not run. */
+int pyc_b200_last_plan(const pyc_ir_module* module, char* out, size_t out_size);
+
+/* The device-arena plan pyc_cuda_dispatch would use for this module and these tensor descriptors, without running
+ * anything (host-only; works without a GPU): one pyc_alloc_request per arena-resident tensor -- tensor_id = IR op id,
+ * size, alignment 1024, start/end = first and last step that touches it -- in placement order, the offset each got, and
+ * the peak.  The placement is the first-fit reuse rule of PyC's planner (src/compiler/runtime/runtime_allocator.c:123-187):
+ * feeding the same requests to pyc_alloc_plan_build_with_mode gives the same offsets and peak.  tensors_on_device != 0
+ * plans as if every tensor were a device pointer (no staging copies), 0 as if all were host memory.
+ * Writes at most `capacity` entries, *count_out = number of arena tensors.  Returns 0 / -1. */
+int pyc_b200_plan_arena(const pyc_ir_module* module, const pyc_tensor* inputs, size_t input_count,
+                        pyc_tensor* outputs, size_t output_count, int tensors_on_device,
+                        pyc_alloc_request* requests_out, size_t* offsets_out, size_t capacity,
+                        size_t* count_out, size_t* peak_bytes_out);
 
 /* Device arena / graph cache telemetry for the last pyc_cuda_dispatch on the
  * current device. */

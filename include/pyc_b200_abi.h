@@ -11,6 +11,7 @@
  *   pyc_backend, pyc_kernel_*_family, pyc_kernel_desc include/pyc/kernel_registry.h:16-51
  *   pyc_alloc_request, pyc_alloc_plan                include/pyc/runtime_allocator.h:14-36
  *   pyc_cuda_dispatch_trace, status codes            include/pyc/cuda_backend.h:28-55
+ *   pyc_collective_comm, pyc_reduce_op, pyc_comm_status include/pyc/collective_comm.h:13-101
  *
  * When this header is compiled inside the PyC tree (the maintainer defines
  * PYC_B200_WITH_PYC_HEADERS), the PyC headers provide the types and this file
@@ -29,6 +30,7 @@
 #include "pyc/compiler_api.h"
 #include "pyc/cuda_backend.h"
 #include "pyc/runtime_allocator.h"
+#include "pyc/collective_comm.h"
 
 #else /* stand-alone declarations */
 
@@ -88,6 +90,19 @@ typedef struct {
     pyc_kernel_hardware_family preferred_hardware_family;
 } pyc_kernel_desc;                  /* 240 bytes */
 
+/* selection trace and context of pyc_kernel_coselect_with_context (kernel_registry.h:53-76) */
+typedef struct {
+    double selected_score, selected_estimated_utilization, pressure_penalty, allocator_penalty, reuse_bonus;
+    size_t candidates_considered;
+} pyc_kernel_selection_trace;       /* 48 bytes */
+
+typedef struct {
+    double pressure_score;
+    size_t pressure_events, rematerialized_tensors, reused_allocations, total_requested_bytes, peak_bytes, memory_budget_bytes;
+    pyc_kernel_workload_family workload_family;
+    pyc_kernel_hardware_family hardware_family;
+} pyc_kernel_coselect_context;      /* 64 bytes */
+
 /* ---- allocation plan (runtime_allocator.h) ------------------------------ */
 enum { PYC_ALLOC_MAX_REQUESTS = 2048 };
 typedef struct { int tensor_id; size_t size_bytes; size_t alignment; int start_step; int end_step; } pyc_alloc_request;
@@ -113,6 +128,27 @@ typedef struct {
 typedef int (*pyc_cpu_executor_fn)(const pyc_ir_module* module, const pyc_tensor* inputs, size_t input_count,
                                    pyc_tensor* outputs, size_t output_count, void* executor_ctx);
 
+/* ---- collective interface (collective_comm.h:13-101) --------------------- */
+typedef enum { PYC_REDUCE_SUM = 0, PYC_REDUCE_PROD = 1, PYC_REDUCE_MIN = 2, PYC_REDUCE_MAX = 3, PYC_REDUCE_AVG = 4 } pyc_reduce_op;
+typedef enum { PYC_COMM_OK = 0, PYC_COMM_ERR_TIMEOUT = 1, PYC_COMM_ERR_HARDWARE = 2, PYC_COMM_ERR_INVALID = 3 } pyc_comm_status;
+typedef void* pyc_comm_handle_t;
+typedef struct pyc_collective_comm {
+    void* backend_ctx;
+    pyc_comm_status (*all_reduce)(void* backend_ctx, pyc_comm_handle_t comm, const void* send_buf, void* recv_buf, size_t count,
+                                  pyc_dtype dtype, pyc_reduce_op op, void* stream);
+    pyc_comm_status (*all_gather)(void* backend_ctx, pyc_comm_handle_t comm, const void* send_buf, void* recv_buf, size_t count,
+                                  pyc_dtype dtype, void* stream);
+    pyc_comm_status (*reduce_scatter)(void* backend_ctx, pyc_comm_handle_t comm, const void* send_buf, void* recv_buf, size_t count,
+                                      pyc_dtype dtype, pyc_reduce_op op, void* stream);
+    pyc_comm_status (*broadcast)(void* backend_ctx, pyc_comm_handle_t comm, const void* send_buf, void* recv_buf, size_t count,
+                                 pyc_dtype dtype, int root_rank, void* stream);
+    pyc_comm_status (*send)(void* backend_ctx, pyc_comm_handle_t comm, const void* send_buf, size_t count, pyc_dtype dtype,
+                            int peer_rank, void* stream);
+    pyc_comm_status (*recv)(void* backend_ctx, pyc_comm_handle_t comm, void* recv_buf, size_t count, pyc_dtype dtype,
+                            int peer_rank, void* stream);
+    pyc_comm_status (*barrier)(void* backend_ctx, pyc_comm_handle_t comm, void* stream);
+} pyc_collective_comm;              /* 64 bytes: context + seven entry points */
+
 #ifdef __cplusplus
 }
 #endif
@@ -131,6 +167,9 @@ PYC_B200_STATIC_ASSERT(sizeof(pyc_ir_module) == 188424, "pyc_ir_module layout");
 PYC_B200_STATIC_ASSERT(sizeof(pyc_tensor) == 96, "pyc_tensor layout");
 PYC_B200_STATIC_ASSERT(sizeof(pyc_kernel_desc) == 240, "pyc_kernel_desc layout");
 PYC_B200_STATIC_ASSERT(sizeof(pyc_cuda_dispatch_trace) == 176, "pyc_cuda_dispatch_trace layout");
+PYC_B200_STATIC_ASSERT(sizeof(pyc_kernel_coselect_context) == 64, "pyc_kernel_coselect_context layout");
+PYC_B200_STATIC_ASSERT(sizeof(pyc_kernel_selection_trace) == 48, "pyc_kernel_selection_trace layout");
+PYC_B200_STATIC_ASSERT(sizeof(pyc_collective_comm) == 64, "pyc_collective_comm layout");
 PYC_B200_STATIC_ASSERT(offsetof(pyc_ir_op, dtype) == 68 && offsetof(pyc_ir_op, input_ids) == 144, "pyc_ir_op offsets");
 
 #endif /* PYC_B200_ABI_H */

@@ -19,10 +19,10 @@ EXPORTS = [
     "pyc_cutlass_gemm_dispatch", "pyc_cutlass_conv2d_dispatch", "pyc_cutlass_attention_dispatch",
     "pyc_cutlass_kernel_count", "pyc_cutlass_registry_init",
     # additive
-    "pyc_b200_gemm", "pyc_b200_gemm_static", "pyc_b200_add", "pyc_b200_bias_act", "pyc_b200_layernorm", "pyc_b200_softmax",
+    "pyc_b200_gemm", "pyc_b200_gemm_static", "pyc_b200_gemm_static_status", "pyc_b200_add", "pyc_b200_bias_act", "pyc_b200_layernorm", "pyc_b200_softmax",
     "pyc_b200_reduce_sum", "pyc_b200_quantize_rows", "pyc_b200_layernorm_quantize", "pyc_b200_gemm_fp8",
-    "pyc_b200_ffn_workspace_bytes", "pyc_b200_ffn_block", "pyc_b200_ffn_block_scatter", "pyc_b200_tp_reduce_broadcast",
-    "pyc_b200_symm_alloc", "pyc_b200_symm_open", "pyc_b200_symm_close", "pyc_b200_symm_free", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm",
+    "pyc_b200_ffn_workspace_bytes", "pyc_b200_ffn_block", "pyc_b200_ffn_block_tp", "pyc_b200_ffn_block_scatter", "pyc_b200_tp_reduce_broadcast",
+    "pyc_b200_symm_alloc", "pyc_b200_symm_open", "pyc_b200_symm_close", "pyc_b200_symm_free", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm", "pyc_b200_autotune_db_load", "pyc_b200_last_plan", "pyc_b200_plan_arena",
     "pyc_b200_get_runtime_info", "pyc_b200_set_stream", "pyc_b200_device_status", "pyc_b200_last_error",
     "pyc_b200_shutdown",
 ]
@@ -56,6 +56,7 @@ def load():
     L.pyc_cutlass_registry_init.restype = None
     L.pyc_b200_gemm.argtypes = [C.POINTER(abi.GemmArgs), vp]
     L.pyc_b200_gemm_static.argtypes = [C.POINTER(abi.GemmArgs), vp]
+    L.pyc_b200_gemm_static_status.argtypes = [C.POINTER(C.c_int), vp]
     L.pyc_b200_add.argtypes = [i, vp, vp, vp, sz, vp]
     L.pyc_b200_bias_act.argtypes = [i, vp, vp, i, i, vp, sz, sz, vp]
     L.pyc_b200_layernorm.argtypes = [i, vp, vp, vp, vp, sz, sz, f, vp]
@@ -67,6 +68,9 @@ def load():
     L.pyc_b200_ffn_workspace_bytes.argtypes = [i, i, i]
     L.pyc_b200_ffn_workspace_bytes.restype = sz
     L.pyc_b200_ffn_block.argtypes = [C.POINTER(abi.FfnArgs), vp, sz, vp]
+    L.pyc_b200_ffn_block_tp.argtypes = [C.POINTER(abi.FfnArgs), vp, vp, i, i, vp, sz, vp]
+    L.pyc_b200_autotune_db_load.argtypes = [C.c_char_p]
+    L.pyc_b200_last_plan.argtypes = [C.POINTER(abi.IrModule), C.c_char_p, sz]
     L.pyc_b200_ffn_block_scatter.argtypes = [C.POINTER(abi.FfnArgs), vp, sz, C.POINTER(vp), i, i, vp]
     L.pyc_b200_tp_reduce_broadcast.argtypes = [vp, C.POINTER(vp), i, i, i, i, vp]
     L.pyc_b200_symm_alloc.argtypes = [sz, C.POINTER(vp), C.c_char_p]
@@ -155,6 +159,12 @@ def gemm_static(dtype, M, N, K, A, B, D, add=None, add_mode=abi.ADD_NONE, act=ab
     _check(load().pyc_b200_gemm_static(C.byref(a), stream), "pyc_b200_gemm_static")
 
 
+def gemm_static_status(host_int_ptr, stream=0):
+    """pyc_b200_gemm_static_status: enqueue the copy of the static block's status word into the int at `host_int_ptr`
+    (an address; pinned memory for an asynchronous copy).  Read the int after synchronising `stream`."""
+    _check(load().pyc_b200_gemm_static_status(C.cast(host_int_ptr, C.POINTER(C.c_int)), stream), "pyc_b200_gemm_static_status")
+
+
 def add(dtype, a, b, out, elems, stream=0):
     _check(load().pyc_b200_add(dtype, a, b, out, elems, stream), "pyc_b200_add")
 
@@ -210,6 +220,24 @@ def _ffn_args(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, out, ln_gamm
     a.w2, a.w2_scale, a.b2 = w2, w2_scale, b2
     a.out = out
     return a
+
+
+def ffn_block_tp(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, out, workspace, workspace_bytes, comm, comm_handle, world, rank,
+                 ln_gamma=None, ln_beta=None, b1=None, b2=None, eps=1e-5, stream=0):
+    """pyc_b200_ffn_block_tp: this rank's shard, then one bf16 all-reduce through the pyc_collective_comm vtable at address `comm`."""
+    a = _ffn_args(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, out, ln_gamma, ln_beta, b1, b2, eps)
+    _check(load().pyc_b200_ffn_block_tp(C.byref(a), comm, comm_handle, world, rank, workspace, workspace_bytes, stream), "pyc_b200_ffn_block_tp")
+
+
+def last_plan(module=None):
+    """Text plan of the most recent GPU run of `module` (None: of any module); None if it has not run."""
+    buf = C.create_string_buffer(16384)
+    n = load().pyc_b200_last_plan(C.byref(module) if module is not None else None, buf, len(buf))
+    return None if n < 0 else buf.value.decode()
+
+
+def autotune_db_load(path=None):
+    return load().pyc_b200_autotune_db_load(path.encode() if path else None)
 
 
 def ffn_block_scatter(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, workspace, workspace_bytes, recv_slots, rank,

@@ -13,6 +13,8 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libpyc_b200.so")
+COMM_SRC = os.path.join(HERE, "csrc_comm", "comm_nccl.cpp")
+COMM_LIB = os.path.join(HERE, "libpyc_b200_comm_nccl.so")   # NCCL backend for PyC's collective interface (loaded by path)
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -61,6 +63,13 @@ def build(verbose=False):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    deps = [COMM_SRC] + [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
+    if not os.path.exists(COMM_LIB) or any(os.path.getmtime(d) > os.path.getmtime(COMM_LIB) for d in deps):
+        cmd = [NVCC, "-O2", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden", f"-I{INCLUDE}", "-shared", "-o", COMM_LIB, COMM_SRC,
+               "-cudart", "static", "-ldl"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"comm backend build failed:\n{r.stdout}\n{r.stderr}")
     return LIB
 
 

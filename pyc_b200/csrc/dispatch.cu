@@ -21,7 +21,9 @@
 #include <string.h>
 
 #include <chrono>
+#include <map>
 #include <memory>
+#include <mutex>
 #include <algorithm>
 #include <string>
 #include <vector>
@@ -46,6 +48,10 @@ double now_ms() {
 bool env_true(const char* name) {
     const char* v = getenv(name);
     return v && (!strcmp(v, "1") || !strcmp(v, "true") || !strcmp(v, "TRUE"));
+}
+bool env_is_false_value(const char* name) {
+    const char* v = getenv(name);
+    return v && (!strcmp(v, "0") || !strcmp(v, "false") || !strcmp(v, "FALSE"));
 }
 bool env_default_true(const char* name) {
     const char* v = getenv(name);
@@ -93,6 +99,8 @@ struct Step {
     int M = 0, N = 0, K = 0;
     size_t stage_off = 0;    // offset in the pinned staging buffer (pageable host tensors)
     bool via_stage = false;
+    int op_main = -1, op_add = -1, op_act = -1;   // IR op ids this step stands for (the fused add / activation when absorbed)
+    std::string symbol, chosen_by;                // kernel that ran the step and who picked it (GEMM steps), set at enqueue
 };
 
 struct Plan {
@@ -100,6 +108,8 @@ struct Plan {
     std::vector<Step> steps;
     size_t arena_peak = 0, arena_total = 0, stage_bytes = 0;
     std::string symbol;          // GEMM configuration of the first matmul (for the reason string)
+    std::string description;     // one line per step: kernel symbol and the IR ops it absorbed (pyc_b200_last_plan)
+    uint64_t module_hash = 0;    // content hash of the IR ops alone (no tensor addresses)
     bool all_device = true;
     // Host-tensor pipeline (see plan_pipeline): index of the GEMM step, rows per chunk, chunk count.
     int pipe_gemm = -1, pipe_rows = 0, pipe_chunks = 0;
@@ -199,7 +209,7 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
         plan->all_device = false;
         v.kind = V_TEMP;
         // static_mask only pins lifetimes (pass 3); whether an upload is dropped is decided by the caller per run.
-        Step s; s.kind = S_H2D; s.out = static_cast<int>(i); s.ext = v.ext; s.bytes = v.bytes;
+        Step s; s.kind = S_H2D; s.out = static_cast<int>(i); s.ext = v.ext; s.bytes = v.bytes; s.op_main = static_cast<int>(i);
         s.via_stage = in_mem[v.ext] == MEM_PAGEABLE;
         if (s.via_stage) { s.stage_off = plan->stage_bytes; plan->stage_bytes = align_up(plan->stage_bytes + v.bytes, 256); }
         S.push_back(s);
@@ -220,6 +230,7 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
             const int c = sole_consumer(cur);
             if (c >= 0 && (m->ops[c].kind == PYC_IR_OP_RELU || m->ops[c].kind == PYC_IR_OP_GELU)) {
                 s.act = m->ops[c].kind == PYC_IR_OP_RELU ? PYC_B200_ACT_RELU : PYC_B200_ACT_GELU;
+                s.op_act = c;
                 V[cur].kind = V_ALIAS; V[cur].alias_of = c; done[c] = 1;
                 return c;
             }
@@ -233,7 +244,7 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
         };
         switch (op.kind) {
             case PYC_IR_OP_MATMUL: {
-                Step s; s.kind = S_GEMM; s.in0 = op.input_ids[0]; s.in1 = op.input_ids[1];
+                Step s; s.kind = S_GEMM; s.in0 = op.input_ids[0]; s.in1 = op.input_ids[1]; s.op_main = static_cast<int>(i);
                 s.M = static_cast<int>(V[i].dims[0]); s.N = static_cast<int>(V[i].dims[1]); s.K = static_cast<int>(V[s.in0].dims[1]);
                 int cur = static_cast<int>(i);
                 const int c = sole_consumer(cur);
@@ -242,7 +253,7 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
                     const bool ready = other != cur && (m->ops[other].kind == PYC_IR_OP_INPUT || static_cast<size_t>(other) < i);
                     const int mode = ready ? classify_add(V[cur], V[other]) : -1;
                     if (mode > 0 && V[other].elems <= V[cur].elems) {
-                        s.add_mode = mode; s.in2 = other;
+                        s.add_mode = mode; s.in2 = other; s.op_add = c;
                         V[cur].kind = V_ALIAS; V[cur].alias_of = c; done[c] = 1;
                         cur = c;
                     }
@@ -257,7 +268,7 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
                 const int big = V[a].elems >= V[b].elems ? a : b, small = big == a ? b : a;
                 const int mode = classify_add(V[big], V[small]);
                 if (mode < 0) return 1;
-                Step s; s.in0 = big; s.in1 = small;
+                Step s; s.in0 = big; s.in1 = small; s.op_main = static_cast<int>(i);
                 int cur = static_cast<int>(i);
                 s.cols = static_cast<size_t>(V[big].dims[V[big].rank - 1]); s.rows = V[big].elems / s.cols;
                 s.kind = S_BIAS_ACT; s.add_mode = mode;
@@ -268,7 +279,7 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
                 break;
             }
             case PYC_IR_OP_RELU: case PYC_IR_OP_GELU: {
-                Step s; s.kind = S_BIAS_ACT; s.in0 = op.input_ids[0]; s.add_mode = PYC_B200_ADD_NONE;
+                Step s; s.kind = S_BIAS_ACT; s.in0 = op.input_ids[0]; s.add_mode = PYC_B200_ADD_NONE; s.op_main = static_cast<int>(i);
                 s.act = op.kind == PYC_IR_OP_RELU ? PYC_B200_ACT_RELU : PYC_B200_ACT_GELU;
                 s.cols = static_cast<size_t>(V[i].dims[V[i].rank - 1]); s.rows = V[i].elems / s.cols;
                 s.out = static_cast<int>(i); V[i].kind = V_TEMP;
@@ -276,7 +287,7 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
                 break;
             }
             case PYC_IR_OP_LAYERNORM: {
-                Step s; s.kind = S_LAYERNORM; s.in0 = op.input_ids[0];
+                Step s; s.kind = S_LAYERNORM; s.in0 = op.input_ids[0]; s.op_main = static_cast<int>(i);
                 s.in1 = op.input_count > 1 ? op.input_ids[1] : -1; s.in2 = op.input_count > 2 ? op.input_ids[2] : -1;
                 s.cols = static_cast<size_t>(V[i].dims[V[i].rank - 1]); s.rows = V[i].elems / s.cols;
                 if (s.in1 >= 0 && V[s.in1].elems != s.cols) return 1;
@@ -288,7 +299,7 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
             case PYC_IR_OP_REDUCE_SUM: {
                 const Value& a = V[op.input_ids[0]];
                 if (a.elems % V[i].elems) return 1;
-                Step s; s.kind = S_REDUCE_SUM; s.in0 = op.input_ids[0]; s.rows = V[i].elems; s.cols = a.elems / V[i].elems;
+                Step s; s.kind = S_REDUCE_SUM; s.in0 = op.input_ids[0]; s.rows = V[i].elems; s.cols = a.elems / V[i].elems; s.op_main = static_cast<int>(i);
                 s.out = static_cast<int>(i); V[i].kind = V_TEMP;
                 S.push_back(s);
                 break;
@@ -303,10 +314,10 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
                 if (V[src].kind == V_TEMP && V[src].consumers == 1 && out_mem[o] == MEM_DEVICE && m->ops[src].kind != PYC_IR_OP_INPUT) {
                     V[src].kind = V_OUTPUT_DIRECT; V[src].ext = o;  // the producing kernel writes the caller's buffer
                 } else if (out_mem[o] == MEM_DEVICE) {
-                    Step s; s.kind = S_COPY; s.in0 = src; s.ext = o; s.bytes = V[src].bytes;
+                    Step s; s.kind = S_COPY; s.in0 = src; s.ext = o; s.bytes = V[src].bytes; s.op_main = static_cast<int>(i);
                     S.push_back(s);
                 } else if (!skip_out_copy) {
-                    Step s; s.kind = S_D2H; s.in0 = src; s.ext = o; s.bytes = V[src].bytes;
+                    Step s; s.kind = S_D2H; s.in0 = src; s.ext = o; s.bytes = V[src].bytes; s.op_main = static_cast<int>(i);
                     s.via_stage = out_mem[o] == MEM_PAGEABLE;
                     if (s.via_stage) { s.stage_off = plan->stage_bytes; plan->stage_bytes = align_up(plan->stage_bytes + s.bytes, 256); }
                     S.push_back(s);
@@ -447,6 +458,7 @@ int enqueue_pipelined(Plan& plan, DeviceContext* ctx, const pyc_tensor* inputs, 
         const GemmConfig* cfg = choose_gemm_config(p);
         if (!cfg) { set_error("no GEMM configuration for %zux%dx%d", rc, gemm.N, gemm.K); return -1; }
         if (plan.symbol.empty()) plan.symbol = gemm_symbol(dt, *cfg);
+        if (c == 0) { plan.steps[plan.pipe_gemm].symbol = gemm_symbol(dt, *cfg); plan.steps[plan.pipe_gemm].chosen_by = last_selection_source(); }
         if (launch_gemm(*cfg, p, stream) != 0) return -1;
         ++*kernels;
         B200_CUDA_OK(cudaEventRecord(ev[3 + chunks + c], stream));
@@ -466,7 +478,7 @@ int enqueue_plan(Plan& plan, DeviceContext* ctx, const pyc_tensor* inputs, pyc_t
         B200_CUDA_OK(cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, stream));
         return 0;
     }
-    for (const Step& s : plan.steps) {
+    for (Step& s : plan.steps) {
         switch (s.kind) {
             case S_H2D: {
                 const void* src = s.via_stage ? static_cast<const void*>(static_cast<char*>(ctx->pinned) + s.stage_off) : inputs[s.ext].data;
@@ -492,6 +504,7 @@ int enqueue_plan(Plan& plan, DeviceContext* ctx, const pyc_tensor* inputs, pyc_t
                 const GemmConfig* cfg = choose_gemm_config(p);
                 if (!cfg) { set_error("no GEMM configuration for %dx%dx%d", s.M, s.N, s.K); return -1; }
                 if (plan.symbol.empty()) plan.symbol = gemm_symbol(p.dtype, *cfg);
+                s.symbol = gemm_symbol(p.dtype, *cfg); s.chosen_by = last_selection_source();
                 if (launch_gemm(*cfg, p, stream) != 0) return -1;
                 ++*kernels;
                 break;
@@ -526,6 +539,75 @@ int enqueue_plan(Plan& plan, DeviceContext* ctx, const pyc_tensor* inputs, pyc_t
     return 0;
 }
 
+// ---- what ran: the sidecar plan ---------------------------------------------------------------------------------
+// PyC's own fusion pass is lossy (pass_manager.c:241-267 renames ops to "matmul_fused" and drops the epilogue) and its
+// kernel catalog for that key holds placeholders (compiler_api.c:2094-2122), so pyc_run_stats.selected_kernel_symbol
+// cannot name the kernel that ran.  The backend therefore keeps, per module content, a text plan: one line per step with
+// the kernel symbol, who chose it, and the IR ops the step absorbed.  pyc_b200_last_plan() returns it.
+const char* kind_name(pyc_ir_op_kind k) {
+    switch (k) {
+        case PYC_IR_OP_INPUT: return "input"; case PYC_IR_OP_CONST: return "const"; case PYC_IR_OP_MATMUL: return "matmul";
+        case PYC_IR_OP_ADD: return "add"; case PYC_IR_OP_RELU: return "relu"; case PYC_IR_OP_GELU: return "gelu";
+        case PYC_IR_OP_REDUCE_SUM: return "reduce_sum"; case PYC_IR_OP_LAYERNORM: return "layernorm"; case PYC_IR_OP_OUTPUT: return "output";
+        default: return "op";
+    }
+}
+const char* dtype_name(pyc_dtype d) { return d == PYC_DTYPE_F32 ? "f32" : d == PYC_DTYPE_BF16 ? "bf16" : d == PYC_DTYPE_F16 ? "f16" : "raw"; }
+
+uint64_t module_content_hash(const pyc_ir_module* module) {
+    uint64_t h = 1469598103934665603ull;
+    h = fnv1a(h, &module->op_count, sizeof(module->op_count));
+    for (size_t i = 0; i < module->op_count; ++i) {
+        const pyc_ir_op& op = module->ops[i];
+        h = fnv1a(h, &op.kind, sizeof(op.kind));
+        h = fnv1a(h, &op.dtype, sizeof(op.dtype));
+        h = fnv1a(h, &op.shape.rank, sizeof(op.shape.rank));
+        h = fnv1a(h, op.shape.dims, sizeof(int64_t) * op.shape.rank);
+        h = fnv1a(h, &op.input_count, sizeof(op.input_count));
+        h = fnv1a(h, op.input_ids, sizeof(int) * op.input_count);
+    }
+    return h;
+}
+
+std::string describe_plan(const Plan& plan, const pyc_ir_module* m) {
+    std::string out;
+    char buf[320];
+    auto op_ref = [&](int id) { char b[96]; snprintf(b, sizeof(b), "%s#%d", kind_name(m->ops[id].kind), id); return std::string(b); };
+    for (size_t si = 0; si < plan.steps.size(); ++si) {
+        const Step& s = plan.steps[si];
+        std::string kernel, ops = s.op_main >= 0 ? op_ref(s.op_main) : std::string("?");
+        const pyc_dtype dt = s.out >= 0 ? plan.values[resolve(plan.values, s.out)].dtype : (s.in0 >= 0 ? plan.values[resolve(plan.values, s.in0)].dtype : PYC_DTYPE_UNKNOWN);
+        switch (s.kind) {
+            case S_H2D: kernel = "copy_h2d"; break;
+            case S_D2H: kernel = "copy_d2h"; break;
+            case S_COPY: kernel = "copy_d2d"; break;
+            case S_GEMM: kernel = s.symbol.empty() ? std::string("b200_gemm_") + dtype_name(dt) : s.symbol; break;
+            case S_ADD: kernel = std::string("b200_add_") + dtype_name(dt); break;
+            case S_BIAS_ACT: kernel = std::string("b200_bias_act_") + dtype_name(dt); break;
+            case S_LAYERNORM: kernel = std::string("b200_layernorm_") + dtype_name(dt); break;
+            case S_REDUCE_SUM: kernel = std::string("b200_reduce_sum_") + dtype_name(dt); break;
+        }
+        if (s.op_add >= 0) ops += " + " + op_ref(s.op_add);
+        if (s.op_act >= 0) ops += " + " + op_ref(s.op_act);
+        if (s.kind == S_GEMM && (int)si == plan.pipe_gemm && plan.pipe_chunks > 1) { snprintf(buf, sizeof(buf), " x%d row chunks", plan.pipe_chunks); ops += buf; }
+        snprintf(buf, sizeof(buf), "step %zu: %s%s%s%s <- %s\n", si, kernel.c_str(), s.chosen_by.empty() ? "" : " [", s.chosen_by.c_str(),
+                 s.chosen_by.empty() ? "" : "]", ops.c_str());
+        out += buf;
+    }
+    return out;
+}
+
+std::mutex g_plan_table_mu;
+std::map<uint64_t, std::string> g_plan_table;   // module content hash -> plan text of its most recent run
+std::string g_last_plan_text;
+
+void publish_plan(const Plan& plan) {
+    std::lock_guard<std::mutex> lk(g_plan_table_mu);
+    if (g_plan_table.size() >= 256 && !g_plan_table.count(plan.module_hash)) g_plan_table.clear();
+    g_plan_table[plan.module_hash] = plan.description;
+    g_last_plan_text = plan.description;
+}
+
 // 0 = ran, 1 = unsupported module (fall back), -1 = error.
 int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_in, pyc_tensor* outputs, size_t n_out,
                pyc_cuda_dispatch_trace* trace, char* reason, size_t reason_size) {
@@ -552,9 +634,31 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
         base = fnv1a(base, &op.input_count, sizeof(op.input_count));
         base = fnv1a(base, op.input_ids, sizeof(int) * op.input_count);
     }
-    for (size_t i = 0; i < n_in; ++i) { base = fnv1a(base, &inputs[i].data, sizeof(void*)); base = fnv1a(base, &inputs[i].size_bytes, sizeof(size_t)); base = fnv1a(base, &in_mem[i], sizeof(MemKind)); }
-    for (size_t i = 0; i < n_out; ++i) { base = fnv1a(base, &outputs[i].data, sizeof(void*)); base = fnv1a(base, &outputs[i].size_bytes, sizeof(size_t)); base = fnv1a(base, &out_mem[i], sizeof(MemKind)); }
+    // Tensor descriptors: address, size, where the memory lives, and the dtype/shape the planner reads when the INPUT op
+    // itself carries none (two calls that differ only there must not share a plan).
+    auto hash_tensor = [&](const pyc_tensor& t, MemKind mk) {
+        base = fnv1a(base, &t.data, sizeof(void*)); base = fnv1a(base, &t.size_bytes, sizeof(size_t)); base = fnv1a(base, &mk, sizeof(MemKind));
+        base = fnv1a(base, &t.dtype, sizeof(t.dtype)); base = fnv1a(base, &t.shape.rank, sizeof(t.shape.rank));
+        base = fnv1a(base, t.shape.dims, sizeof(int64_t) * (t.shape.rank <= PYC_IR_MAX_DIMS ? t.shape.rank : PYC_IR_MAX_DIMS));
+    };
+    for (size_t i = 0; i < n_in; ++i) hash_tensor(inputs[i], in_mem[i]);
+    for (size_t i = 0; i < n_out; ++i) hash_tensor(outputs[i], out_mem[i]);
     base = fnv1a(base, &skip_out, sizeof(skip_out));
+    // Switches that change which kernel a captured graph holds.
+    for (const char* name : {"PYC_B200_AUTOTUNE", "PYC_B200_GEMM_L2_HINTS", "PYC_B200_GEMM_GROUP_M", "PYC_CUDA_BF16_GEMM_SYMBOL",
+                             "PYC_CUDA_ENABLE_PROMOTED_GEMM", "PYC_B200_REGISTRY_SELECT"}) {
+        const char* v = getenv(name);
+        base = fnv1a(base, name, strlen(name));
+        if (v) base = fnv1a(base, v, strlen(v) + 1);
+    }
+    {
+        const uint64_t epoch = selection_epoch();   // a new autotune winner invalidates graphs captured with the old choice
+        base = fnv1a(base, &epoch, sizeof(epoch));
+        if (!env_is_false_value("PYC_CUDA_ENABLE_PROMOTED_GEMM")) {
+            std::string promoted;                   // so does a promotion made through PyC's registry since the capture
+            if (registry_promoted_symbol("matmul", &promoted)) base = fnv1a(base, promoted.data(), promoted.size());
+        }
+    }
     // PYC_B200_PIPELINE_HOST_COPIES=0 keeps uploads, kernel and downloads strictly one after another.
     const bool pipeline_enabled = env_default_true("PYC_B200_PIPELINE_HOST_COPIES");
     base = fnv1a(base, &pipeline_enabled, sizeof(pipeline_enabled));
@@ -594,7 +698,7 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
             for (const Step& st : plan_holder->steps)
                 if (st.kind == S_GEMM) {
                     const pyc_dtype dt = plan_holder->values[resolve(plan_holder->values, st.out)].dtype;
-                    if (!has_gemm_winner(dt, st.M, st.N, st.K)) autotune_gemm_unlocked(ctx, dt, st.M, st.N, st.K, 3, nullptr, nullptr);
+                    if (!has_gemm_winner(dt, st.M, st.N, st.K)) autotune_gemm_unlocked(ctx, dt, st.M, st.N, st.K, 5, nullptr, nullptr, st.add_mode, st.act);
                 }
         }
     }
@@ -647,10 +751,13 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
     } else {
         if (enqueue_plan(plan, ctx, inputs, outputs, launch_stream, &kernels) != 0) { snprintf(reason, reason_size, "b200_launch_failed:%.100s", last_error()); return -1; }
     }
+    if (plan.description.empty()) { plan.module_hash = module_content_hash(module); plan.description = describe_plan(plan, module); }
+    publish_plan(plan);
     ctx->last_graph_kernels = kernels;
     ctx->last_plan_total = plan.arena_total;
-    ctx->last_base = base;
-    ctx->resident_base = want_static ? base : 0;
+    // Until this run is known to have succeeded nothing counts as resident: a failed upload must not be skipped next time.
+    ctx->last_base = 0;
+    ctx->resident_base = 0;
     if (trace) { trace->kernel_ms = now_ms() - t0; trace->graph_replayed = replayed ? 1 : 0; }
 
     if (!async) {
@@ -670,6 +777,9 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
             if (s.kind == S_D2H && s.via_stage) memcpy(outputs[s.ext].data, static_cast<char*>(ctx->pinned) + s.stage_off, s.bytes);
         if (trace) trace->copy_out_ms = now_ms() - t0;
     }
+    // Success (in async mode: everything was enqueued without error): the static operands of this key are in the arena.
+    ctx->last_base = base;
+    ctx->resident_base = want_static ? base : 0;
     const char* mode = !replay_enabled ? "b200_stream" : replayed ? "b200_graph_replay" : "b200_graph_capture";
     if (plan.symbol.empty()) snprintf(reason, reason_size, "%s", mode);
     else snprintf(reason, reason_size, "%s:%s", mode, plan.symbol.c_str());
@@ -766,6 +876,49 @@ pyc_cuda_dispatch_status pyc_cuda_dispatch(const pyc_ir_module* module, const py
         else set_reason(trace, why);
     }
     return PYC_CUDA_DISPATCH_FALLBACK;
+}
+
+
+int pyc_b200_plan_arena(const pyc_ir_module* module, const pyc_tensor* inputs, size_t input_count, pyc_tensor* outputs, size_t output_count,
+                        int tensors_on_device, pyc_alloc_request* requests_out, size_t* offsets_out, size_t capacity, size_t* count_out,
+                        size_t* peak_bytes_out) {
+    if (!module || !inputs || !outputs || !count_out) { set_error("pyc_b200_plan_arena: NULL argument"); return -1; }
+    const MemKind kind = tensors_on_device ? MEM_DEVICE : MEM_PAGEABLE;
+    std::vector<MemKind> in_mem(input_count, kind), out_mem(output_count, kind);
+    Plan plan;
+    const int rc = build_plan(module, inputs, input_count, outputs, output_count, in_mem, out_mem, false, 0u, &plan);
+    if (rc != 0) { set_error(rc > 0 ? "pyc_b200_plan_arena: module uses an op the GPU path does not know" : "pyc_b200_plan_arena: malformed module or tensors"); return -1; }
+    size_t n = 0;
+    for (size_t i = 0; i < plan.values.size(); ++i) {
+        const Value& v = plan.values[i];
+        if (v.kind != V_TEMP) continue;
+        if (n < capacity && requests_out && offsets_out) {
+            requests_out[n].tensor_id = static_cast<int>(i);
+            requests_out[n].size_bytes = v.bytes;
+            requests_out[n].alignment = 1024;
+            requests_out[n].start_step = v.def_step;
+            requests_out[n].end_step = v.last_step;
+            offsets_out[n] = v.arena_off;
+        }
+        ++n;
+    }
+    *count_out = n;
+    if (peak_bytes_out) *peak_bytes_out = plan.arena_peak;
+    return 0;
+}
+
+int pyc_b200_last_plan(const pyc_ir_module* module, char* out, size_t out_size) {
+    std::lock_guard<std::mutex> lk(g_plan_table_mu);
+    const std::string* text = nullptr;
+    if (module) {
+        auto it = g_plan_table.find(module_content_hash(module));
+        if (it != g_plan_table.end()) text = &it->second;
+    } else if (!g_last_plan_text.empty()) {
+        text = &g_last_plan_text;
+    }
+    if (!text) { set_error("pyc_b200_last_plan: this module has not run on the GPU in this process"); return -1; }
+    if (out && out_size) { strncpy(out, text->c_str(), out_size - 1); out[out_size - 1] = '\0'; }
+    return static_cast<int>(text->size());
 }
 
 }  // extern "C"

@@ -496,3 +496,20 @@ extern "C" int pyc_b200_gemm_static(const pyc_b200_gemm_args* a, void* stream) {
     if (best_bn == 128) return launch_static_layout<128, 6>(p, s, sd, 1);
     return launch_static_layout<64, 8>(p, s, sd, 2);
 }
+
+// Allocation-free reader of the static block's status word.  The kernel's bounded waits record a code there when they
+// give up; without this a caller of pyc_b200_gemm_static could not tell a timed-out GEMM from a good one, because the
+// ordinary status call reads the per-device context (and creating that context allocates).
+extern "C" int pyc_b200_gemm_static_status(int* host_out, void* stream) {
+    using namespace b200;
+    if (!host_out) { set_error("pyc_b200_gemm_static_status: NULL destination"); return -1; }
+    int dev = 0;
+    B200_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16 || !g_static_setup[dev].ready) {
+        // Nothing has been launched through the static entry on this device: there is nothing to report.
+        *host_out = 0;
+        return 0;
+    }
+    B200_CUDA_OK(cudaMemcpyAsync(host_out, g_static_setup[dev].scratch, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+    return 0;
+}

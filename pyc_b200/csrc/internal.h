@@ -79,6 +79,14 @@ const GemmConfig* find_gemm_config(const char* symbol);
 const GemmConfig* choose_gemm_config(const GemmProblem& p);
 void remember_gemm_winner(pyc_dtype dtype, int M, int N, int K, const GemmConfig* cfg);
 bool gemm_config_supports(const GemmConfig& cfg, const GemmProblem& p);
+// Who made the last choose_gemm_config() decision of this thread: "autotune", "env", "promoted", "registry" or "model".
+const char* last_selection_source();
+// Bumped whenever a per-shape winner changes; part of the dispatch layer's graph-cache key.
+uint64_t selection_epoch();
+// PyC's workload classes for a matmul shape (compiler_api.c:1141-1170).
+pyc_kernel_workload_family matmul_workload_family(size_t m, size_t n, size_t k);
+// Load persisted timings / per-shape winners (path NULL: PYC_AUTOTUNE_DB_PATH).  Returns winners installed, -1 without a path.
+int autotune_db_load(const char* path);
 
 int launch_gemm(const GemmConfig& cfg, const GemmProblem& p, cudaStream_t stream);
 // kernel-file entry points

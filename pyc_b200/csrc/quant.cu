@@ -63,9 +63,10 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
     return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
 }
 
-// VPT vectors of 8 bf16 per thread cached (cols <= QT*8*VPT); cols % 8 == 0.
+// VPT vectors of 8 bf16 per thread cached (cols <= QT*8*VPT); cols % 8 == 0.  The widest form keeps 32 registers of raw
+// row data per thread, so it is built for two resident CTAs per SM (128 registers) instead of four (64, which spilled).
 template <int VPT, bool LN>
-__global__ void __launch_bounds__(QT, 4)
+__global__ void __launch_bounds__(QT, VPT >= 8 ? 2 : (VPT >= 4 && LN) ? 3 : 4)
 rowquant_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
                 uint8_t* __restrict__ q, float* __restrict__ scale, size_t rows, size_t cols, float eps) {
     __shared__ float scratch[8];
@@ -249,6 +250,28 @@ static int ffn_block_impl(const pyc_b200_ffn_args* a, void* workspace, size_t wo
 
 int pyc_b200_ffn_block(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* stream) {
     return ffn_block_impl(a, workspace, workspace_bytes, stream, nullptr);
+}
+
+// Tensor-parallel block through PyC's collective interface (include/pyc/collective_comm.h:30-42): this rank's shard of
+// the block, then ONE all-reduce (sum) of the [tokens, hidden] bf16 partial sums, issued through the caller's vtable on
+// the same stream.  The communicator handle is whatever the launcher created for that backend (PyC passes it around as
+// "comm_handle", distributed_runtime.c:16-42).
+int pyc_b200_ffn_block_tp(const pyc_b200_ffn_args* a, const pyc_collective_comm* comm, pyc_comm_handle_t comm_handle, int world, int rank,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+    if (!a) { set_error("ffn tp: NULL arguments"); return -1; }
+    if (world < 1 || rank < 0 || rank >= world) { set_error("ffn tp: bad world/rank %d/%d", rank, world); return -1; }
+    if (world > 1 && (!comm || !comm->all_reduce || !comm_handle)) { set_error("ffn tp: world %d needs a collective vtable with all_reduce and a communicator handle", world); return -1; }
+    if (!a->out) { set_error("ffn tp: NULL output"); return -1; }
+    if (ffn_block_impl(a, workspace, workspace_bytes, stream, nullptr) != 0) return -1;
+    if (world == 1) return 0;
+    const size_t count = static_cast<size_t>(a->tokens) * static_cast<size_t>(a->hidden);
+    const pyc_comm_status st = comm->all_reduce(comm->backend_ctx, comm_handle, a->out, a->out, count, PYC_DTYPE_BF16, PYC_REDUCE_SUM, stream);
+    if (st != PYC_COMM_OK) {
+        set_error("ffn tp: all_reduce through the collective vtable failed with pyc_comm_status %d (%s)", static_cast<int>(st),
+                  st == PYC_COMM_ERR_TIMEOUT ? "timeout" : st == PYC_COMM_ERR_HARDWARE ? "hardware/transport" : "invalid argument or unsupported dtype");
+        return -1;
+    }
+    return 0;
 }
 
 int pyc_b200_ffn_block_scatter(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* const* recv_slots, int world, int rank,

@@ -57,6 +57,7 @@ struct DeviceContext {
 DeviceContext* current_context();
 std::string gemm_symbol(pyc_dtype d, const GemmConfig& c);
 bool has_gemm_winner(pyc_dtype dtype, int M, int N, int K);
-int autotune_gemm_unlocked(DeviceContext* ctx, pyc_dtype dtype, int M, int N, int K, int iters, std::string* best_symbol, double* best_ms);
+int autotune_gemm_unlocked(DeviceContext* ctx, pyc_dtype dtype, int M, int N, int K, int iters, std::string* best_symbol, double* best_ms,
+                           int add_mode = PYC_B200_ADD_NONE, int act = PYC_B200_ACT_NONE);
 
 }  // namespace b200

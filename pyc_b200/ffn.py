@@ -6,16 +6,21 @@ Partitioning (Megatron style): rank r of g holds the column slice W1[:, r*I/g:(r
 slice W2[r*I/g:(r+1)*I/g, :]; the LayerNorm input is replicated; GELU is local; every rank produces a partial [T,H]
 and ONE all-reduce (sum, bf16) per block finishes it.  Two ways to do that all-reduce:
 
-  * exchange="nccl": pyc_b200_ffn_block, then torch.distributed.all_reduce (NCCL over NVLink);
+  * exchange="nccl": pyc_b200_ffn_block_tp -- the block, then one all_reduce through PyC's collective vtable
+    (include/pyc/collective_comm.h:30-42), served by libpyc_b200_comm_nccl.so (NCCL over NVLink, bf16 mapped);
   * exchange="peer": no library collective.  The second GEMM's epilogue stores each row of the partial sum straight into
     the receive buffer of the rank that owns the row (reduce-scatter by plain stores into peer memory, overlapped with the
     GEMM tile by tile), a reduction kernel adds the received slices and stores the owned rows into every rank's output
-    (the all-gather, again plain peer stores).  Ranks are ordered by two stream barriers (a one-element NCCL all-reduce
-    each); no kernel waits on another GPU.  Buffers are made visible to the other processes with CUDA IPC.
+    (the all-gather, again plain peer stores).  Ranks are ordered by two stream barriers (the vtable's barrier, on the
+    same stream as the kernels); no kernel waits on another GPU.  Buffers are made visible to the other processes with CUDA IPC.
 
-The compute is the C-ABI library; torch.distributed is the plumbing (handle exchange, barriers, the NCCL variant).  PyC itself implements no parallel strategy: its options
+The compute and the collective calls are the C-ABI library; torch.distributed only carries the bootstrap (NCCL unique
+id, IPC handles) between the processes.  PyC itself implements no parallel strategy: its options
 struct carries world_size/rank (include/pyc/compiler_api.h:53-62) but pyc_run_model never calls a collective.
 """
+import ctypes as C
+import os
+
 import numpy as np
 
 from . import backend
@@ -35,14 +40,67 @@ def shard_weights(w1, s1, w2, rank, world, b1=None):
     return out + ((np.ascontiguousarray(b1[lo:hi]),) if b1 is not None else ())
 
 
+class CollectiveBackend:
+    """A loaded collective backend (pyc_comm_backend_create of a shared library that implements PyC's
+    pyc_collective_comm, include/pyc/collective_comm.h:93-101) plus one communicator for the ranks of `group`.
+
+    The default library is this package's NCCL backend; the communicator is bootstrapped here (rank 0 draws the NCCL
+    unique id, torch.distributed carries it to the others) because PyC expects its launcher to bring one."""
+
+    DEFAULT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libpyc_b200_comm_nccl.so")
+
+    def __init__(self, torch, group=None, path=None, config_json="{}"):
+        dist = torch.distributed
+        self.torch, self.group = torch, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        path = path or self.DEFAULT
+        if not os.path.exists(path):
+            raise backend.BackendError(f"{path} is missing: run `python -m pyc_b200.build`")
+        L = self.lib = C.CDLL(path)
+        L.pyc_comm_backend_create.argtypes = [C.c_char_p]; L.pyc_comm_backend_create.restype = C.c_void_p
+        L.pyc_comm_backend_destroy.argtypes = [C.c_void_p]; L.pyc_comm_backend_destroy.restype = None
+        L.pyc_b200_nccl_unique_id.argtypes = [C.c_void_p, C.c_char_p]
+        L.pyc_b200_nccl_comm_init_rank.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
+        L.pyc_b200_nccl_comm_destroy.argtypes = [C.c_void_p, C.c_void_p]
+        L.pyc_b200_nccl_last_error.argtypes = [C.c_void_p]; L.pyc_b200_nccl_last_error.restype = C.c_char_p
+        self.vtable = L.pyc_comm_backend_create(config_json.encode())
+        if not self.vtable:
+            raise backend.BackendError("pyc_comm_backend_create returned NULL")
+        ident = C.create_string_buffer(128)
+        if self.rank == 0 and L.pyc_b200_nccl_unique_id(self.vtable, ident) != 0:
+            raise backend.BackendError(f"NCCL unique id: {self.error()}")
+        box = [ident.raw]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        handle = C.c_void_p()
+        if L.pyc_b200_nccl_comm_init_rank(self.vtable, box[0], self.world, self.rank, C.byref(handle)) != 0:
+            raise backend.BackendError(f"ncclCommInitRank: {self.error()}")
+        self.handle = handle.value
+        # the seven entry points of the vtable, for the calls this module makes itself (the barriers of the peer exchange)
+        fn = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_void_p)
+        words = (C.c_void_p * 8).from_address(self.vtable)
+        self._ctx, self._barrier = words[0], fn(words[7])
+
+    def error(self):
+        return (self.lib.pyc_b200_nccl_last_error(self.vtable) or b"").decode()
+
+    def barrier(self, stream):
+        st = self._barrier(self._ctx, self.handle, stream)
+        if st != 0:
+            raise backend.BackendError(f"collective barrier failed with pyc_comm_status {st}: {self.error()}")
+
+    def close(self):
+        if self.vtable:
+            self.torch.cuda.synchronize()
+            if self.handle:
+                self.lib.pyc_b200_nccl_comm_destroy(self.vtable, self.handle)
+            self.lib.pyc_comm_backend_destroy(self.vtable)
+            self.vtable = self.handle = None
+
+
 class FfnBlock:
-    """Device-resident shard of one FFN block plus its workspace; call run() once per step.
+    """Device-resident shard of one FFN block plus its workspace; call run() once per step."""
 
-    With more than one rank the tokens can be processed in `chunks` row slices: the all-reduce of slice i runs on a
-    second stream while slice i+1 is still in its GEMMs.  Measured on 2/4/8 B200s this loses to the unsliced block
-    (four times the launches, smaller GEMMs, one NCCL call per slice: 0.79 vs 0.64 ms at 2 ranks), so the default is 1."""
-
-    def __init__(self, tokens, hidden, inner_local, w1, s1, w2, s2, torch, group=None, chunks=None, exchange="nccl"):
+    def __init__(self, tokens, hidden, inner_local, w1, s1, w2, s2, torch, group=None, exchange="nccl", comm=None):
         self.torch, self.group = torch, group
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
@@ -54,55 +112,39 @@ class FfnBlock:
         self.s2 = torch.from_numpy(np.ascontiguousarray(s2, dtype=np.float32)).to(dev)
         dist = torch.distributed
         self.parallel = group is not None or (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1)
-        if chunks is None:
-            chunks = 1
-        if tokens % chunks:
-            raise ValueError(f"{tokens} tokens do not split into {chunks} equal chunks")
-        self.chunks, self.rows = chunks, tokens // chunks
-        self.ws_bytes = backend.ffn_workspace_bytes(self.rows, hidden, inner_local)
-        # one workspace per chunk in flight: chunk i+1 may start while chunk i's output is still being reduced,
-        # but its scratch is free as soon as its last GEMM has been issued on the same stream
+        self.world = dist.get_world_size(group) if self.parallel else 1
+        self.rank = dist.get_rank(group) if self.parallel else 0
+        self.ws_bytes = backend.ffn_workspace_bytes(tokens, hidden, inner_local)
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
         self.out = torch.zeros((tokens, hidden), dtype=torch.bfloat16, device=dev)
-        self.comm_stream = torch.cuda.Stream() if self.parallel and chunks > 1 else None
-        self.peer = None
+        self.comm, self._own_comm, self.peer = comm, False, None
+        if self.parallel and self.comm is None:
+            self.comm, self._own_comm = CollectiveBackend(torch, group), True
         if exchange == "peer" and self.parallel:
-            if chunks != 1:
-                raise ValueError("exchange='peer' works on the whole block (chunks=1)")
-            self.peer = PeerExchange(tokens, hidden, torch, group)
+            self.peer = PeerExchange(tokens, hidden, torch, self.comm, group)
 
     def run(self, x_dev, stream=None):
-        """x_dev: [T,H] bf16 (or int16 bit pattern) device tensor.  Returns the (all-reduced) bf16 output tensor."""
-        torch = self.torch
-        cur = torch.cuda.current_stream()
-        s = stream if stream is not None else cur.cuda_stream
-        row_bytes = self.hidden * 2
+        """x_dev: [T,H] bf16 (or int16 bit pattern) device tensor.  Every kernel, the all-reduce and the barriers are
+        enqueued on `stream` (default: torch's current stream).  Returns the (all-reduced) bf16 output tensor."""
+        s = stream if stream is not None else self.torch.cuda.current_stream().cuda_stream
         if self.peer is not None:
             px = self.peer
             backend.ffn_block_scatter(self.tokens, self.hidden, self.inner, x_dev.data_ptr(), self.w1.data_ptr(), self.s1.data_ptr(),
                                       self.w2.data_ptr(), self.s2.data_ptr(), self.ws.data_ptr(), self.ws_bytes, px.recv_ptrs, px.rank, stream=s)
-            px.barrier()            # every rank's slices have landed (kernel completion makes peer stores visible)
+            self.comm.barrier(s)    # every rank's slices have landed (kernel completion makes peer stores visible)
             backend.tp_reduce_broadcast(px.recv_ptrs[px.rank], px.out_ptrs, px.rank, px.rows, self.hidden, stream=s)
-            px.barrier()            # every rank has written its rows into this rank's output
+            self.comm.barrier(s)    # every rank has written its rows into this rank's output
             return px.out
-        for c in range(self.chunks):
-            off = c * self.rows
-            backend.ffn_block(self.rows, self.hidden, self.inner, x_dev.data_ptr() + off * row_bytes, self.w1.data_ptr(), self.s1.data_ptr(),
-                              self.w2.data_ptr(), self.s2.data_ptr(), self.out.data_ptr() + off * row_bytes, self.ws.data_ptr(), self.ws_bytes, stream=s)
-            if not self.parallel:
-                continue
-            part = self.out[off:off + self.rows]
-            if self.comm_stream is None:
-                torch.distributed.all_reduce(part, group=self.group)
-            else:
-                ev = torch.cuda.Event()
-                ev.record(cur)
-                self.comm_stream.wait_event(ev)
-                with torch.cuda.stream(self.comm_stream):
-                    torch.distributed.all_reduce(part, group=self.group)
-        if self.comm_stream is not None:
-            cur.wait_stream(self.comm_stream)
+        backend.ffn_block_tp(self.tokens, self.hidden, self.inner, x_dev.data_ptr(), self.w1.data_ptr(), self.s1.data_ptr(),
+                             self.w2.data_ptr(), self.s2.data_ptr(), self.out.data_ptr(), self.ws.data_ptr(), self.ws_bytes,
+                             self.comm.vtable if self.comm else None, self.comm.handle if self.comm else None, self.world, self.rank, stream=s)
         return self.out
+
+    def close(self):
+        if self.peer is not None:
+            self.peer.close(); self.peer = None
+        if self._own_comm and self.comm is not None:
+            self.comm.close(); self.comm = None
 
 
 class _DeviceView:
@@ -115,9 +157,9 @@ class _DeviceView:
 class PeerExchange:
     """Receive buffer [world][T/world][H] and output [T][H] (bf16) of this rank, mapped into every other rank's process."""
 
-    def __init__(self, tokens, hidden, torch, group=None):
+    def __init__(self, tokens, hidden, torch, comm, group=None):
         dist = torch.distributed
-        self.torch, self.group = torch, group
+        self.torch, self.group, self.comm = torch, group, comm
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if tokens % self.world:
             raise ValueError(f"{tokens} tokens do not split over {self.world} ranks")
@@ -136,12 +178,7 @@ class PeerExchange:
                 self._opened += [p_recv, p_out]
                 self.recv_ptrs.append(p_recv); self.out_ptrs.append(p_out)
         self.out = torch.as_tensor(_DeviceView(self._own[1][0], (tokens, hidden), "<i2"), device="cuda").view(torch.bfloat16)
-        self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
         dist.barrier(group=group)
-
-    def barrier(self):
-        # stream-ordered: completes on this rank's stream only after every rank's stream has reached its own call
-        self.torch.distributed.all_reduce(self._token, op=self.torch.distributed.ReduceOp.MAX, group=self.group)
 
     def close(self):
         self.torch.cuda.synchronize()

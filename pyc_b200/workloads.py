@@ -33,13 +33,30 @@ def uniform(shape, seed, lo=-1.0, hi=1.0):
     return (lo + (hi - lo) * uniform01(n, seed)).astype(np.float32).reshape(shape)
 
 
-def normal(shape, seed, std=1.0):
-    """Box-Muller on two decorrelated streams of the same seed."""
-    n = int(np.prod(shape))
-    u1 = uniform01(n, seed)
-    u2 = uniform01(n, seed ^ 0xA5A5A5A5A5A5A5A5)
+def _normal_span(lo, hi, seed, std):
+    u1 = uniform01(hi - lo, seed, lo)
+    u2 = uniform01(hi - lo, seed ^ 0xA5A5A5A5A5A5A5A5, lo)
     r = np.sqrt(-2.0 * np.log(1.0 - u1))
-    return (std * r * np.cos(2.0 * np.pi * u2)).astype(np.float32).reshape(shape)
+    return (std * r * np.cos(2.0 * np.pi * u2)).astype(np.float32)
+
+
+def normal(shape, seed, std=1.0):
+    """Box-Muller on two decorrelated streams of the same seed.  Element i depends only on (seed, i), so large tensors
+    are drawn in spans on a few threads (numpy releases the GIL) with the same values as one pass."""
+    n = int(np.prod(shape))
+    span = 1 << 21
+    if n <= span:
+        return _normal_span(0, n, seed, std).reshape(shape)
+    from concurrent.futures import ThreadPoolExecutor
+    import os
+    out = np.empty(n, np.float32)
+
+    def fill(lo):
+        out[lo:min(n, lo + span)] = _normal_span(lo, min(n, lo + span), seed, std)
+
+    with ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as ex:
+        list(ex.map(fill, range(0, n, span)))
+    return out.reshape(shape)
 
 
 def to_bf16_bits(x):
@@ -87,15 +104,15 @@ _E4M3_POS = E4M3_VALUES[:127].astype(np.float64)   # codes 0x00..0x7E ascending,
 
 
 def e4m3_encode(x):
-    """fp32 -> e4m3 codes, round to nearest even, saturating at +-448."""
+    """fp32 -> e4m3 codes, round to nearest even, saturating at +-448 (integer arithmetic on the fp32 bit pattern)."""
     x = np.ascontiguousarray(x, dtype=np.float32)
-    ax = np.minimum(np.abs(x).astype(np.float64), 448.0)
-    hi = np.searchsorted(_E4M3_POS, ax, side="left").clip(1, 126)
-    lo = hi - 1
-    dlo, dhi = ax - _E4M3_POS[lo], _E4M3_POS[hi] - ax
-    pick_hi = (dhi < dlo) | ((dhi == dlo) & (hi % 2 == 0))
-    code = np.where(pick_hi, hi, lo).astype(np.uint8)
-    return (code | (np.signbit(x).astype(np.uint8) << 7)).astype(np.uint8)
+    ax = np.minimum(np.abs(x), np.float32(448.0))
+    u = ax.view(np.uint32)
+    r = u + (np.uint32(0x7FFFF) + ((u >> np.uint32(20)) & np.uint32(1)))          # round the mantissa to 3 bits, ties to even
+    normal = (((r >> np.uint32(23)) - np.uint32(120)) << np.uint32(3)) | ((r >> np.uint32(20)) & np.uint32(7))
+    sub = np.rint(ax * np.float32(512.0)).astype(np.uint32)                        # below 2^-6: multiples of 2^-9 (8 -> code 0x08 = 2^-6)
+    code = np.where(ax < np.float32(2.0 ** -6), sub, normal).astype(np.uint8)
+    return code | (np.signbit(x).astype(np.uint8) << np.uint8(7))
 
 
 def e4m3_decode(codes):

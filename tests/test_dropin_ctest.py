@@ -12,9 +12,18 @@ REF = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 
 BINARIES = sorted(glob.glob(os.path.join(REF, "ctest_*")))
 
 
+def _skip_if_needs_missing_sources(path):
+    # test_pass_golden reads a golden file from PyC's own source tree (path compiled in); where that tree is not present
+    # (a machine that only received the built binaries) it cannot run.
+    root_file = os.path.join(REF, "ref_root.txt")
+    if path.endswith("test_pass_golden") and os.path.exists(root_file) and not os.path.isdir(open(root_file).read().strip()):
+        pytest.skip("PyC's source tree (golden file) is not on this machine")
+
+
 @pytest.mark.skipif(not BINARIES, reason="PyC's tests were not built (no PyC checkout at build time)")
 @pytest.mark.parametrize("path", BINARIES, ids=[os.path.basename(p) for p in BINARIES])
 def test_pyc_ctest_passes_against_this_backend(path, tmp_path):
+    _skip_if_needs_missing_sources(path)
     env = dict(os.environ)
     for k in ["PYC_CUDA_DISABLE", "PYC_CUDA_FORCE_ERROR", "PYC_CUDA_FORCE_FALLBACK", "PYC_CUDA_SIMULATE_AVAILABLE"]:
         env.pop(k, None)

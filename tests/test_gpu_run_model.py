@@ -68,6 +68,9 @@ BINARIES = sorted(glob.glob(os.path.join(os.path.dirname(oracle.REF_FRONT_SO), "
 
 @pytest.mark.parametrize("path", BINARIES, ids=[os.path.basename(p) for p in BINARIES])
 def test_pyc_ctest_on_the_gpu(path, tmp_path):
+    root_file = os.path.join(os.path.dirname(path), "ref_root.txt")
+    if path.endswith("test_pass_golden") and os.path.exists(root_file) and not os.path.isdir(open(root_file).read().strip()):
+        pytest.skip("PyC's source tree (golden file) is not on this machine")
     env = dict(os.environ)
     env["PYC_AUTOTUNE_DB_PATH"] = str(tmp_path / "autotune.db")
     r = subprocess.run([path], cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=180)

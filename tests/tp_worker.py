@@ -1,0 +1,61 @@
+"""Worker for the multi-GPU tensor-parallel FFN test: one process per GPU (torchrun), benchmark configuration 5's block
+with the inner dimension sharded over the ranks.  Both exchanges run -- the all-reduce through PyC's collective vtable
+(NCCL backend) and the peer-store exchange -- and EACH result is compared with the CPU oracle's unsharded block on sampled
+token rows (fp8 tolerance 6e-2, norm-wise).  Prints one line per rank and exchange that the test parses.
+
+    python -m torch.distributed.run --nproc-per-node 2 ... tests/tp_worker.py --tokens 1024 --hidden 1024 --inner 4096
+"""
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import oracle  # noqa: E402  (checker)
+from pyc_b200 import backend, ffn, workloads  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=1024); ap.add_argument("--hidden", type=int, default=1024); ap.add_argument("--inner", type=int, default=4096)
+    ap.add_argument("--rows", type=int, default=48, help="token rows compared with the oracle")
+    a = ap.parse_args()
+    world, rank, local = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    backend.load()
+    xb, w1, s1, w2, s2 = workloads.ffn_inputs(a.tokens, a.hidden, a.inner)
+    rng = np.random.default_rng(5)
+    per = a.tokens // world
+    rows = sorted(set([0, a.tokens - 1] + [r * per + d for r in range(world) for d in (0, per - 1)] +
+                      rng.integers(0, a.tokens, a.rows).tolist()))
+    want = oracle.ffn_reference(oracle.Oracle(), workloads.bf16_bits_to_f32(xb[rows]), w1, s1, w2, s2)
+    w1r, s1r, w2r = ffn.shard_weights(w1, s1, w2, rank, world)
+    X = torch.from_numpy(xb.view(np.int16)).cuda()
+    comm = ffn.CollectiveBackend(torch)
+    ok = True
+    for exchange in ("nccl", "peer"):
+        blk = ffn.FfnBlock(a.tokens, a.hidden, a.inner // world, w1r, s1r, w2r, s2, torch, exchange=exchange, comm=comm)
+        for _ in range(2):
+            out = blk.run(X)
+        torch.cuda.synchronize()
+        assert backend.device_status() == 0
+        got = out[rows].float().cpu().numpy()
+        err = float(np.abs(got - want).max() / np.abs(want).max())
+        print(f"tp_worker rank {rank}/{world} exchange {exchange}: max_rel_err_vs_oracle {err:.4e} rows {len(rows)}", flush=True)
+        ok = ok and err <= 6e-2
+        dist.barrier()
+        blk.close()
+    comm.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()
