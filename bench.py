@@ -1,13 +1,15 @@
 #!/usr/bin/env python
 """Benchmark of the hot path: one fused GEMM graph through the PyC backend seam.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extras] [--no-cpu-baseline]
 
-Workload (N=1): benchmark configuration 2 -- M=N=K=8192 bf16 ~N(0,1)*0.02, fp32
-accumulate, bias[8192] + exact GELU epilogue, bf16 output -- as the IR module
-matmul -> add -> gelu run through pyc_cuda_dispatch.  A step is one run of that
-graph.  With N GPUs every rank runs its own independent graph (weak scaling, no
-collective on the data path).  One JSON line is printed by rank 0.
+Headline workload (N=1): benchmark configuration 2 -- M=N=K=8192 bf16 ~N(0,1)*0.02, fp32 accumulate, bias[8192] + exact
+GELU epilogue, bf16 output -- as the IR module matmul -> add -> gelu run through pyc_cuda_dispatch.  A step is one run of
+that graph.  With N GPUs every rank runs its own independent graph (weak scaling, no collective on the data path).
+Rank 0 prints ONE JSON line.  Its `extra` object carries, from the same run, the other benchmark configurations (1: graph
+latency, 3: causal attention, 4a/4b: conv2d, 5: fp8 FFN block -- tensor-parallel over the N ranks when N > 1), the
+HBM-bound ops and a seconds-long sustained loop of the headline graph, each with its time, rate, roofline fraction and the
+error of a sample of its result against the CPU oracle.
 """
 import argparse
 import json
@@ -24,9 +26,7 @@ sys.path.insert(0, ROOT)
 M = N = K = 8192
 FLOP_PER_STEP = 2.0 * M * N * K
 ALGO_BYTES = 3 * M * N * 2 + N * 2          # A, B, D bf16 + bias
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of this exact shape, from the ncu capture summarised in
-# profiles/gemm_tc_bf16_8192x8192x8192_traffic.md (the CTA-pair kernel the dispatch picks for this shape; update both together
-# when the kernel changes).
+# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of the default kernel (b200_gemm_bf16_tc2_256x256x64_s6)
 NCU_TRAFFIC_BYTES = 1104316160 + 126199296
 METRIC = "fused bf16 GEMM+bias+GELU TFLOP/s via pyc_cuda_dispatch"
 
@@ -97,25 +97,47 @@ class ClockSampler:
 
     def end(self):
         self.windows.append((self._t0, time.perf_counter()))
+        return self.windows[-1]
 
-    def stop(self):
-        self._stop = True
-        if self.thread:
-            self.thread.join(timeout=2)
+    def summary(self, windows=None):
+        windows = self.windows if windows is None else windows
         if self.err and not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.err]}
-        inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in self.windows)]
+        inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in windows)]
         mhz = sorted(s[1] for s in inside)
         bits = 0
         for s in inside:
             bits |= int(s[2])
-        nv = self.nv
         names = [("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4),
                  ("hw_power_brake", 0x80), ("sync_boost", 0x10), ("applications_clocks_setting", 0x2)]
         reasons = [n for n, m in names if bits & m]
         watts = [s[3] for s in inside if s[3] is not None]
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_min_mhz": mhz[0] if mhz else None, "sm_max_mhz": self.max_mhz,
                 "reasons": reasons, "samples": len(mhz), "power_w_max": max(watts) if watts else None}
+
+    def stop(self):
+        self._stop = True
+        if self.thread:
+            self.thread.join(timeout=2)
+        return self.summary()
+
+
+def bind_near_gpu(local):
+    """Run this process (and allocate its pinned buffers) on the CPU cores NVML reports as close to its GPU.  A process
+    setting; nothing on the GPU changes.  Returns the number of cores, or None when NVML gives no answer."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cores = [64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1]
+        cores = [c for c in cores if c in os.sched_getaffinity(0)]
+        if cores:
+            os.sched_setaffinity(0, cores)
+            return len(cores)
+    except Exception:
+        pass
+    return None
 
 
 def build_problem(torch, rank):
@@ -203,6 +225,311 @@ def reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------------------------
+# extras: the other configurations, measured in the same run
+# ------------------------------------------------------------------------------------------------------------------
+class Extras:
+    """Each entry: {ms, tflops | gbs | us_p50/us_p95, frac, peak_source, max_rel_err_vs_oracle_sample, ...}.
+    Inputs of these legs are drawn on the device (torch generator, fixed seeds) with the distributions the benchmark
+    configurations name; what the CPU oracle needs for its sample is copied back.  Timing: CUDA events on the launching
+    stream around every single launch, an L2 flush (256 MiB write) before each one unless the working set exceeds L2."""
+
+    def __init__(self, torch, backend, abi, rank, world, sampler, host_barrier):
+        import oracle
+        self.torch, self.backend, self.abi, self.rank, self.world, self.sampler = torch, backend, abi, rank, world, sampler
+        self.host_barrier = host_barrier
+        self.orc = oracle.Oracle()
+        self.oracle = oracle
+        self.burst, self.sustained_tf, self.hbm, self.src = measured_peaks()
+        self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        self.out = {}
+
+    def bits(self, t):
+        return t.view(self.torch.int16)
+
+    def f32(self, t):
+        return t.float().cpu().numpy()
+
+    def time_launch(self, run, iters=20, warmup=3, flush=True):
+        torch = self.torch
+        for _ in range(warmup):
+            run()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+        self.sampler.begin()
+        for e0, e1 in ev:
+            if flush:
+                self.flush_buf.zero_()
+            e0.record()
+            run()
+            e1.record()
+        torch.cuda.synchronize()
+        self.sampler.end()
+        ts = sorted(e0.elapsed_time(e1) for e0, e1 in ev)
+        assert self.backend.device_status() == 0, "a kernel wait timed out"
+        return sum(ts) / len(ts), ts[len(ts) // 2]
+
+    @staticmethod
+    def rel_err(got, want):
+        want = np.asarray(want, np.float64)
+        return float(np.abs(np.asarray(got, np.float64) - want).max() / max(np.abs(want).max(), 1e-30))
+
+    def guarded(self, name, fn):
+        try:
+            fn()
+        except Exception as e:  # an extra leg must never take the headline line down with it
+            self.out[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+
+    # -- configuration 1: graph latency of the 512^3 fp32 matmul -> add -> relu module through pyc_cuda_dispatch
+    def config1_latency(self, calls=300):
+        torch, backend, abi = self.torch, self.backend, self.abi
+        from pyc_b200 import ir, workloads
+        m = 512
+        x, w, b = workloads.gemm_inputs(1, m, m, m, ("uniform", -1.0, 1.0))
+        dev = [torch.from_numpy(t).cuda() for t in (x, w, b)]
+        out = torch.zeros((m, m), dtype=torch.float32, device="cuda")
+        host = [torch.from_numpy(t).pin_memory() for t in (x, w, b)]
+        hout = torch.zeros((m, m), dtype=torch.float32).pin_memory()
+        module = ir.matmul_bias_act(abi.DTYPE_F32, m, m, m, bias="row", act="relu")
+        want = self.orc.relu(self.orc.add(self.orc.matmul(x, w), b))
+
+        def tens(ts, o):
+            return ([backend.make_tensor(t.data_ptr(), t.numel() * 4, abi.DTYPE_F32, tuple(t.shape)) for t in ts],
+                    [backend.make_tensor(o.data_ptr(), o.numel() * 4, abi.DTYPE_F32, (m, m))])
+        backend.set_stream(None, async_=False)
+        res = {"workload": "config 1: X[512,512] W[512,512] b[512] fp32, matmul->add->relu, one graph replay + sync per call",
+               "l2": "warm (latency configuration, 3 MB working set)", "calls": calls}
+        for label, (ins, outs), o in (("device_tensors", tens(dev, out), out), ("pinned_host_tensors", tens(host, hout), hout)):
+            for _ in range(30):
+                backend.dispatch(module, ins, outs)
+            ts = []
+            for _ in range(calls):
+                t0 = time.perf_counter()
+                st, trace = backend.dispatch(module, ins, outs)
+                ts.append((time.perf_counter() - t0) * 1e6)
+            ts.sort()
+            got = o.cpu().numpy() if label == "device_tensors" else o.numpy()
+            res[label] = {"us_p50": ts[len(ts) // 2], "us_p95": ts[int(len(ts) * 0.95)], "us_min": ts[0], "kernel": trace.reason.decode(),
+                          "max_rel_err_vs_oracle_sample": self.rel_err(got, want)}
+        # the graph alone on the device: replays enqueued without synchronising, CUDA events around each
+        backend.set_stream(torch.cuda.current_stream().cuda_stream, async_=True)
+        d_ins, d_outs = tens(dev, out)
+        mean, med = self.time_launch(lambda: backend.dispatch(module, d_ins, d_outs), iters=100, flush=False)
+        backend.set_stream(None, async_=False)
+        res["graph_device_us"] = {"mean": mean * 1e3, "median": med * 1e3}
+        self.out["config1_latency"] = res
+
+    # -- configuration 3: causal attention, batch 8 x 32 heads x 2048 x 128, bf16
+    def config3_attention(self, batch_heads=256, seq=2048, d=128):
+        torch, backend, abi = self.torch, self.backend, self.abi
+        g = torch.Generator(device="cuda"); g.manual_seed(0x5EED0030 + self.rank)
+        q, k, v = (torch.randn((batch_heads, seq, d), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16) for _ in range(3))
+        o = torch.zeros_like(q)
+        run = lambda: backend.attention(abi.DTYPE_BF16, batch_heads, seq, d, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d ** -0.5, 1)
+        mean, med = self.time_launch(run, iters=20, flush=False)   # 537 MB working set > L2
+        heads = [0, batch_heads - 1]
+        want = np.stack([self.orc.attention(self.f32(q[h]), self.f32(k[h]), self.f32(v[h]), d ** -0.5, True) for h in heads])
+        got = np.stack([self.f32(o[h]) for h in heads])
+        flop = 4.0 * batch_heads * d * seq * (seq + 1) / 2
+        tf = flop / (mean * 1e-3) / 1e12
+        self.out["config3_attention"] = {"workload": f"config 3: causal attention {batch_heads} heads x {seq} x {d} bf16, scale 1/sqrt({d}), fp32 statistics",
+                                         "ms": mean, "ms_median": med, "tflops": tf, "frac": tf / self.burst, "peak_source": f"{self.src} burst cuBLAS bf16",
+                                         "algorithmic_flop": flop, "l2": "working set 537 MB > L2",
+                                         "max_rel_err_vs_oracle_sample": self.rel_err(got, want), "oracle_sample": "heads 0 and last, all rows"}
+
+    # -- configuration 4: conv2d NHWC 3x3 + bias + ReLU, bf16
+    def config4_conv(self):
+        torch, backend, abi = self.torch, self.backend, self.abi
+        for name, (n, h, c) in (("config4a_conv", (64, 56, 64)), ("config4b_conv", (256, 14, 256))):
+            g = torch.Generator(device="cuda"); g.manual_seed(0x5EED0040 + c)
+            x = (torch.rand((n, h, h, c), generator=g, device="cuda") * 2 - 1).to(torch.bfloat16)
+            w = (torch.randn((c, 3, 3, c), generator=g, device="cuda") * (2.0 / (9 * c)) ** 0.5).to(torch.bfloat16)
+            b = (torch.randn((c,), generator=g, device="cuda") * 0.1).to(torch.bfloat16)
+            o = torch.zeros((n, h, h, c), dtype=torch.bfloat16, device="cuda")
+            run = lambda: backend.conv2d(abi.DTYPE_BF16, n, h, h, c, c, 3, 3, (1, 1), (1, 1), x.data_ptr(), w.data_ptr(), b.data_ptr(), True, o.data_ptr())
+            mean, med = self.time_launch(run, iters=30, flush=True)
+            imgs = [0, n - 1]
+            want = self.orc.conv2d(self.f32(x[imgs]), self.f32(w), self.f32(b), relu=True)
+            flop = 2.0 * n * h * h * c * c * 9
+            tf = flop / (mean * 1e-3) / 1e12
+            nbytes = (2 * n * h * h * c + 9 * c * c + c) * 2
+            self.out[name] = {"workload": f"conv2d NHWC N={n} H=W={h} C_in=C_out={c} 3x3 s1 p1 bf16 + bias + ReLU", "ms": mean, "ms_median": med,
+                              "tflops": tf, "frac": tf / self.burst, "peak_source": f"{self.src} burst cuBLAS bf16", "algorithmic_flop": flop,
+                              "gbs": nbytes / (mean * 1e-3) / 1e9, "frac_hbm": nbytes / (mean * 1e-3) / 1e9 / self.hbm, "l2": "flushed before every launch",
+                              "max_rel_err_vs_oracle_sample": self.rel_err(self.f32(o[imgs]), want), "oracle_sample": "first and last image"}
+
+    # -- HBM-bound ops
+    def elementwise(self, rows=16384, cols=8192):
+        torch, backend, abi = self.torch, self.backend, self.abi
+        g = torch.Generator(device="cuda"); g.manual_seed(0x5EED0060)
+        res = {}
+        for dt_name, dt, tdt in (("bf16", abi.DTYPE_BF16, torch.bfloat16), ("f32", abi.DTYPE_F32, torch.float32)):
+            x = torch.randn((rows, cols), generator=g, device="cuda").to(tdt); y = torch.randn((rows, cols), generator=g, device="cuda").to(tdt)
+            bias = torch.randn((cols,), generator=g, device="cuda").to(tdt); o = torch.zeros_like(x)
+            n, es = rows * cols, x.element_size()
+            ops = {"add": (lambda: backend.add(dt, x.data_ptr(), y.data_ptr(), o.data_ptr(), n), 3,
+                           lambda s: self.orc.add(self.f32(x[s]), self.f32(y[s]))),
+                   "bias_gelu": (lambda: backend.bias_act(dt, x.data_ptr(), bias.data_ptr(), abi.ADD_ROW_BIAS, abi.ACT_GELU, o.data_ptr(), rows, cols), 2,
+                                 lambda s: self.orc.gelu(self.orc.add(self.f32(x[s]), self.f32(bias)))),
+                   "layernorm": (lambda: backend.layernorm(dt, x.data_ptr(), None, None, o.data_ptr(), rows, cols), 2,
+                                 lambda s: self.orc.layernorm(self.f32(x[s]))),
+                   "softmax": (lambda: backend.softmax(dt, x.data_ptr(), o.data_ptr(), rows, cols), 2,
+                               lambda s: self.orc.softmax(self.f32(x[s])))}
+            sample = slice(rows - 8, rows)
+            for op, (run, passes, want_fn) in ops.items():
+                mean, med = self.time_launch(run, iters=10, flush=False)    # 2-3 tensors of 268/537 MB > L2
+                gbs = passes * n * es / (mean * 1e-3) / 1e9
+                tol = 1e-5 if dt == abi.DTYPE_F32 else 2e-2
+                res[f"{op}_{dt_name}"] = {"ms": mean, "gbs": gbs, "frac": gbs / self.hbm, "max_rel_err_vs_oracle_sample": self.rel_err(self.f32(o[sample]), want_fn(sample)),
+                                          "tolerance": tol}
+            del x, y, o
+        res["workload"] = f"[{rows},{cols}] tensors, bytes = reads + writes (add 3x, others 2x)"
+        res["peak_source"] = f"{self.src} copy bandwidth {self.hbm} GB/s"
+        self.out["elementwise"] = res
+
+    # -- sustained loop of the headline graph
+    def sustained(self, dispatch_once, seconds=2.5):
+        torch = self.torch
+        stream = torch.cuda.current_stream()
+        steps = max(200, int(seconds / 0.8e-3))
+        for _ in range(20):
+            dispatch_once()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.sampler.begin()
+        e0.record(stream)
+        for _ in range(steps):
+            dispatch_once()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        win = self.sampler.end()
+        ms = e0.elapsed_time(e1) / steps
+        tf = FLOP_PER_STEP / (ms * 1e-3) / 1e12
+        clk = self.sampler.summary([win])
+        self.out["sustained"] = {"workload": "config 2 graph replayed back to back", "steps": steps, "seconds": ms * steps * 1e-3, "ms_per_step": ms,
+                                 "tflops": tf, "frac": tf / self.sustained_tf, "peak_source": f"{self.src} sustained cuBLAS bf16",
+                                 "sm_mhz_median": clk.get("sm_mhz"), "power_w_max": clk.get("power_w_max"), "reasons": clk.get("reasons")}
+
+    # -- configuration 5: LayerNorm -> fp8 GEMM + GELU -> fp8 GEMM, one GPU and tensor-parallel
+    def config5_ffn(self, tokens=8192, hidden=4096, inner=16384):
+        torch, backend, abi = self.torch, self.backend, self.abi
+        from pyc_b200 import ffn, workloads
+        dist = torch.distributed
+        world, rank = self.world, self.rank
+        g = torch.Generator(device="cuda"); g.manual_seed(0x5EED0050)          # same weights on every rank
+        x = torch.randn((tokens, hidden), generator=g, device="cuda").to(torch.bfloat16)
+
+        def fp8_weight(k, n):
+            w = torch.randn((k, n), generator=g, device="cuda") * k ** -0.5
+            scale = (w.abs().amax(dim=0) / 448.0).clamp_min(1e-30)
+            codes = (w / scale).to(torch.float8_e4m3fn).view(torch.uint8)
+            return codes, scale.float()
+        w1, s1 = fp8_weight(hidden, inner)
+        w2, s2 = fp8_weight(inner, hidden)
+        w1h, s1h, w2h, s2h = w1.cpu().numpy(), s1.cpu().numpy(), w2.cpu().numpy(), s2.cpu().numpy()
+        rows = sorted(set([0, tokens - 1, tokens // 2] + np.random.default_rng(5).integers(0, tokens, 13).tolist()))
+        want = self.oracle.ffn_reference(self.orc, self.f32(x[rows]), w1h, s1h, w2h, s2h)
+        flop = 4.0 * tokens * hidden * inner
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+
+        def phases(run, iters=5):
+            """Per-phase split from events the block records itself; mean over `iters` calls."""
+            for e in events:
+                e.record()
+            table = backend.ffn_phase_events([e.cuda_event for e in events])
+            acc = np.zeros(4)
+            for _ in range(iters):
+                run()
+                torch.cuda.synchronize()
+                acc += [events[i].elapsed_time(events[i + 1]) for i in range(4)]
+            backend.ffn_phase_events(None)
+            del table
+            return dict(zip(("layernorm_quantize_ms", "gemm1_gelu_ms", "quantize_ms", "gemm2_ms"), (acc / iters).tolist()))
+
+        res = {"workload": f"config 5: tokens {tokens}, hidden {hidden} -> {inner} (GELU) -> {hidden}; x bf16 ~N(0,1), LayerNorm eps 1e-5, "
+                           "W1/W2 e4m3 with one fp32 scale per output channel, activations quantised per token, bf16 out",
+               "algorithmic_flop": flop, "oracle_sample": f"{len(rows)} token rows", "tolerance": 6e-2,
+               "peak_source": f"{self.src} burst cuBLAS bf16 ({self.burst}); frac_fp8 is against twice that (no measured fp8 figure)"}
+        if rank == 0 or world == 1:
+            blk = ffn.FfnBlock(tokens, hidden, inner, w1h, s1h, w2h, s2h, torch, single=True)
+            run = lambda: blk.run(self.bits(x))
+            mean, med = self.time_launch(run, iters=10, flush=False)
+            tf = flop / (mean * 1e-3) / 1e12
+            one = {"ms": mean, "tflops": tf, "frac": tf / self.burst, "frac_fp8": tf / (2 * self.burst),
+                   "max_rel_err_vs_oracle_sample": self.rel_err(self.f32(blk.out[rows]), want)}
+            one.update(phases(run))
+            res["one_gpu"] = one
+            del blk
+        if world > 1:
+            self.host_barrier()
+            comm = ffn.CollectiveBackend(torch)
+            w1r, s1r, w2r = ffn.shard_weights(w1h, s1h, w2h, rank, world)
+            tp = {}
+            for exchange in ("nccl", "peer"):
+                blk = ffn.FfnBlock(tokens, hidden, inner // world, w1r, s1r, w2r, s2h, torch, exchange=exchange, comm=comm)
+                run = lambda: blk.run(self.bits(x))
+                for _ in range(3):
+                    run()
+                torch.cuda.synchronize(); dist.barrier()
+                iters = 20
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(iters):
+                    out = run()
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / iters, self.rel_err(self.f32(out[rows]), want)], dtype=torch.float64, device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms, err = float(t[0]), float(t[1])
+                tf = flop / (ms * 1e-3) / 1e12
+                entry = {"ms": ms, "tflops": tf, "frac_fp8": tf / (2 * self.burst * world), "max_rel_err": err}
+                ph = phases(run)
+                pt = torch.tensor(list(ph.values()), dtype=torch.float64, device="cuda")
+                dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+                entry["phases_max_over_ranks"] = dict(zip(ph.keys(), pt.tolist()))
+                entry["exchange_ms"] = ms - float(pt.sum())      # everything of a step that is not one of the four kernels
+                tp[exchange] = entry
+                dist.barrier()
+                blk.close()
+            # the 67 MB bf16 all-reduce alone, through the same vtable
+            buf = torch.zeros((tokens, hidden), dtype=torch.bfloat16, device="cuda")
+            ar = vtable_all_reduce(comm)
+            s = torch.cuda.current_stream().cuda_stream
+            for _ in range(3):
+                ar(buf.data_ptr(), buf.numel(), self.abi.DTYPE_BF16, s)
+            torch.cuda.synchronize(); dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                ar(buf.data_ptr(), buf.numel(), self.abi.DTYPE_BF16, s)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / 10], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            nbytes = tokens * hidden * 2
+            tp["all_reduce_alone"] = {"ms": float(t[0]), "bytes": nbytes, "bus_gbs": 2.0 * (world - 1) / world * nbytes / (float(t[0]) * 1e-3) / 1e9}
+            tp["world"] = world
+            tp["max_rel_err"] = max(tp["nccl"]["max_rel_err"], tp["peer"]["max_rel_err"])
+            tp["ms"] = min(tp["nccl"]["ms"], tp["peer"]["ms"])
+            comm.close()
+            res_tp = tp
+            self.out["ffn_tp"] = res_tp
+        self.out["config5_ffn"] = res
+
+
+def vtable_all_reduce(comm):
+    """all_reduce entry of a loaded pyc_collective_comm vtable as a Python callable (in place, sum)."""
+    import ctypes as C
+    words = (C.c_void_p * 8).from_address(comm.vtable)
+    fn = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_void_p)(words[1])
+
+    def call(ptr, count, dtype, stream):
+        st = fn(words[0], comm.handle, ptr, ptr, count, dtype, 0, stream)
+        if st != 0:
+            raise RuntimeError(f"all_reduce failed with pyc_comm_status {st}: {comm.error()}")
+    return call
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -210,6 +537,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0")); local = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
@@ -217,15 +545,30 @@ def main():
         return
     args.warmup = max(args.warmup, 3)
 
+    # The CPU baseline runs on rank 0 BEFORE the process group exists: the other ranks wait in the rendezvous on the host,
+    # not inside an NCCL kernel on their GPUs.
+    cpu_line = None
+    if rank == 0 and not args.no_cpu_baseline:
+        cpu_line, _, _ = cpu_baseline()
+
     import torch
     import torch.distributed as dist
     from pyc_b200 import abi, backend, ir
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
     torch.cuda.set_device(local)
+    cores_bound = bind_near_gpu(local) if world > 1 else None
+    host_pg = None
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        host_pg = dist.new_group(backend="gloo")      # waits that must not occupy a GPU (an NCCL barrier spins in a kernel)
+        os.environ.setdefault("PYC_B200_PIPELINE_CHUNKS", "16")
     backend.load()
+
+    def host_barrier():
+        if world > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=host_pg)
 
     host, dev, out_host, out_dev = build_problem(torch, rank)
     module = ir.matmul_bias_act(abi.DTYPE_BF16, M, K, N, bias="row", act="gelu")
@@ -252,34 +595,62 @@ def main():
         st, trace = backend.dispatch(module, ins, outs)
     e1.record(stream)
     barrier()
-    sampler.end()
+    headline_windows = [sampler.end()]
     ms_total = e0.elapsed_time(e1)
     launches = backend.runtime_info().kernel_launches_total - launches0
     assert backend.device_status() == 0, "a kernel wait timed out"
     kernel_symbol = trace.reason.decode()
+    plan_text = backend.last_plan(module)
 
     # ---- end-to-end arm: the same call with pinned HOST tensors; H2D of A, B, bias and D2H of D inside every step
     backend.set_stream(None, async_=False)
     h_ins, h_outs = tensors_for(backend, abi, host, out_host)
     e2e_steps = max(3, min(args.steps, 10))
-    for _ in range(2):
-        backend.dispatch(module, h_ins, h_outs)
-    barrier()
-    sampler.begin()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        backend.dispatch(module, h_ins, h_outs)
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    sampler.end()
-    clocks = sampler.stop()
+
+    def e2e_leg():
+        for _ in range(2):
+            backend.dispatch(module, h_ins, h_outs)
+        barrier()
+        sampler.begin()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            backend.dispatch(module, h_ins, h_outs)
+        barrier()
+        dt = time.perf_counter() - t0
+        headline_windows.append(sampler.end())
+        return dt
+    e2e_s = e2e_leg()
     same = bool((out_host[:64].to(torch.int32) == out_dev[:64].cpu().to(torch.int32)).all())
     e2e_kernels = int(backend.runtime_info().kernels_per_graph)   # > 1: A uploaded in row chunks, copies and GEMMs overlapped
+    # the same leg with the weight and bias treated as what they are -- static: PyC's own switch (cuda_backend.c:2521-2522)
+    os.environ["PYC_CUDA_ASSUME_STATIC_RHS"] = "1"
+    out_host.zero_()
+    e2e_static_s = e2e_leg()
+    os.environ.pop("PYC_CUDA_ASSUME_STATIC_RHS", None)
+    same_static = bool((out_host[:64].to(torch.int32) == out_dev[:64].cpu().to(torch.int32)).all())
+    clocks = sampler.summary(headline_windows)
 
-    times = torch.tensor([ms_total, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+    times = torch.tensor([ms_total, e2e_s * 1e3, e2e_static_s * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms = float(times[0]), float(times[1])
+    ms_total, e2e_ms, e2e_static_ms = float(times[0]), float(times[1]), float(times[2])
+
+    extras = None
+    if not args.no_extras:
+        ex = Extras(torch, backend, abi, rank, world, sampler, host_barrier)
+        backend.set_stream(stream.cuda_stream, async_=True)
+        ex.guarded("sustained", lambda: ex.sustained(lambda: backend.dispatch(module, ins, outs)))
+        backend.set_stream(None, async_=False)
+        del host, h_ins, h_outs, dev, out_dev, ins, outs
+        torch.cuda.empty_cache()
+        ex.guarded("config5_ffn", ex.config5_ffn)       # every rank: tensor-parallel over the N ranks when N > 1
+        if rank == 0:                                    # the other ranks wait on the host (gloo), their GPUs idle
+            ex.guarded("config1_latency", ex.config1_latency)
+            ex.guarded("config3_attention", ex.config3_attention)
+            ex.guarded("config4_conv", ex.config4_conv)
+            ex.guarded("elementwise", ex.elementwise)
+        extras = ex.out
+    sampler.stop()
 
     if rank == 0:
         burst, sustained, hbm, src = measured_peaks()
@@ -287,27 +658,36 @@ def main():
         value = world * FLOP_PER_STEP * args.steps / (ms_total * 1e-3) / 1e12
         per_gpu = FLOP_PER_STEP / (ms_step * 1e-3) / 1e12
         peak = sustained if ms_total > 1000.0 else burst
+        h2d_all, d2h = (M * K + K * N + N) * 2, M * N * 2
+
+        def e2e_obj(ms, h2d):
+            per_step = ms / e2e_steps
+            return {"value": world * FLOP_PER_STEP * e2e_steps / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": e2e_steps, "ms_per_step": per_step,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "host_gbs_all_ranks": world * (h2d + d2h) / (per_step * 1e-3) / 1e9}
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": "config 2: fused GEMM graph M=N=K=8192, bf16 in/out, fp32 accumulate, bias[8192]+GELU(erf) epilogue; "
                                    "one independent graph per GPU", "l2": "inputs (3 x 128 MiB) larger than the 126 MB L2",
-                       "kernel": kernel_symbol, "e2e_matches_device_result": same,
-                       "e2e_row_chunks": e2e_kernels},
+                       "kernel": kernel_symbol, "plan": plan_text, "e2e_matches_device_result": same and same_static,
+                       "e2e_row_chunks": e2e_kernels, "e2e": "A, B and bias uploaded from pinned host memory every step, D downloaded",
+                       "e2e_static_weights": "B kept on the device after the first step (PYC_CUDA_ASSUME_STATIC_RHS=1); A and bias up, D down every step",
+                       "cores_bound_near_gpu": cores_bound},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak,
-                         "traffic": None, "peak_source": f"{src} {'sustained' if peak == sustained else 'burst'} cuBLAS bf16",
+                         "traffic": NCU_TRAFFIC_BYTES, "peak_source": f"{src} {'sustained' if peak == sustained else 'burst'} cuBLAS bf16",
                          "algorithmic_bytes": ALGO_BYTES, "algorithmic_flop": FLOP_PER_STEP},
-            "e2e": {"value": world * FLOP_PER_STEP * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": e2e_steps,
-                    "ms_per_step": e2e_ms / e2e_steps, "h2d_bytes_per_step": (M * K + K * N + N) * 2, "d2h_bytes_per_step": M * N * 2},
+            "e2e": e2e_obj(e2e_ms, h2d_all),
+            "e2e_static_weights": e2e_obj(e2e_static_ms, (M * K + N) * 2),
             "gpu_launches": int(launches), "clocks": clocks,
         }
-        line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES
-        if not args.no_cpu_baseline:
-            line["cpu_baseline"], _, _ = cpu_baseline()
+        if cpu_line is not None:
+            line["cpu_baseline"] = cpu_line
+        if extras is not None:
+            line["extra"] = extras
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
+        host_barrier()
         dist.destroy_process_group()
 
 

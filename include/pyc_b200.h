@@ -217,6 +217,12 @@ typedef struct {
 size_t pyc_b200_ffn_workspace_bytes(int tokens, int hidden, int inner);
 int pyc_b200_ffn_block(const pyc_b200_ffn_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Per-phase timing of the FFN block for profiling callers: events5 points to five cudaEvent_t (created by the caller with
+ * timing enabled) that every following pyc_b200_ffn_block / _tp / _scatter call OF THIS THREAD records on its stream: [0]
+ * at the start, [1] after LayerNorm+quantise, [2] after the first GEMM (+GELU), [3] after the re-quantise, [4] after the
+ * second GEMM.  NULL switches it off again.  Nothing is allocated or synchronised. */
+int pyc_b200_ffn_phase_events(void* const* events5);
+
 /* Tensor-parallel FFN through PyC's collective interface.  Each rank calls this with its shard (as described above:
  * column slice of W1 / b1 / w1_scale, row slice of W2, b2 on one rank) and the vtable of a loaded collective backend
  * (pyc_collective_comm, include/pyc/collective_comm.h:30-101; PyC's loader is pyc_load_comm_backend,

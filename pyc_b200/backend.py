@@ -21,7 +21,7 @@ EXPORTS = [
     # additive
     "pyc_b200_gemm", "pyc_b200_gemm_static", "pyc_b200_gemm_static_status", "pyc_b200_add", "pyc_b200_bias_act", "pyc_b200_layernorm", "pyc_b200_softmax",
     "pyc_b200_reduce_sum", "pyc_b200_quantize_rows", "pyc_b200_layernorm_quantize", "pyc_b200_gemm_fp8",
-    "pyc_b200_ffn_workspace_bytes", "pyc_b200_ffn_block", "pyc_b200_ffn_block_tp", "pyc_b200_ffn_block_scatter", "pyc_b200_tp_reduce_broadcast",
+    "pyc_b200_ffn_workspace_bytes", "pyc_b200_ffn_block", "pyc_b200_ffn_block_tp", "pyc_b200_ffn_phase_events", "pyc_b200_ffn_block_scatter", "pyc_b200_tp_reduce_broadcast",
     "pyc_b200_symm_alloc", "pyc_b200_symm_open", "pyc_b200_symm_close", "pyc_b200_symm_free", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm", "pyc_b200_autotune_db_load", "pyc_b200_last_plan", "pyc_b200_plan_arena",
     "pyc_b200_get_runtime_info", "pyc_b200_set_stream", "pyc_b200_device_status", "pyc_b200_last_error",
     "pyc_b200_shutdown",
@@ -238,6 +238,19 @@ def last_plan(module=None):
 
 def autotune_db_load(path=None):
     return load().pyc_b200_autotune_db_load(path.encode() if path else None)
+
+
+def ffn_phase_events(event_handles):
+    """Five cudaEvent_t handles (ints) recorded by the following FFN block calls of this thread, or None to stop.
+    Returns the ctypes table, which must stay alive while the hook is set."""
+    L = load()
+    L.pyc_b200_ffn_phase_events.argtypes = [C.POINTER(C.c_void_p)]
+    if event_handles is None:
+        L.pyc_b200_ffn_phase_events(None)
+        return None
+    table = (C.c_void_p * 5)(*event_handles)
+    L.pyc_b200_ffn_phase_events(table)
+    return table
 
 
 def ffn_block_scatter(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, workspace, workspace_bytes, recv_slots, rank,

@@ -399,7 +399,11 @@ void plan_pipeline(Plan* plan) {
     if (!a_uploaded) return;
     const size_t moved = plan->values[a].bytes + plan->values[d].bytes;
     if (gemm.M < 1024 || moved < (size_t(32) << 20)) return;
-    int rows = (gemm.M / 8 + 255) / 256 * 256;      // whole 256-row tiles, about eight chunks
+    // Whole 256-row tiles, about eight chunks; PYC_B200_PIPELINE_CHUNKS asks for another count (2..64): more, smaller
+    // chunks help when several processes share one host's PCIe root and memory system.
+    int want_chunks = 8;
+    if (const char* e = getenv("PYC_B200_PIPELINE_CHUNKS")) { const int v = atoi(e); if (v >= 2 && v <= 64) want_chunks = v; }
+    int rows = (gemm.M / want_chunks + 255) / 256 * 256;
     plan->pipe_gemm = g;
     plan->pipe_rows = rows;
     plan->pipe_chunks = (gemm.M + rows - 1) / rows;
@@ -646,7 +650,7 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
     base = fnv1a(base, &skip_out, sizeof(skip_out));
     // Switches that change which kernel a captured graph holds.
     for (const char* name : {"PYC_B200_AUTOTUNE", "PYC_B200_GEMM_L2_HINTS", "PYC_B200_GEMM_GROUP_M", "PYC_CUDA_BF16_GEMM_SYMBOL",
-                             "PYC_CUDA_ENABLE_PROMOTED_GEMM", "PYC_B200_REGISTRY_SELECT"}) {
+                             "PYC_CUDA_ENABLE_PROMOTED_GEMM", "PYC_B200_REGISTRY_SELECT", "PYC_B200_PIPELINE_CHUNKS"}) {
         const char* v = getenv(name);
         base = fnv1a(base, name, strlen(name));
         if (v) base = fnv1a(base, v, strlen(v) + 1);

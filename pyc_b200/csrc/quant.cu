@@ -223,6 +223,14 @@ size_t pyc_b200_ffn_workspace_bytes(int tokens, int hidden, int inner) {
     return align256(T * H) + align256(T * 4) + align256(T * I * 2) + align256(T * I) + align256(T * 4);
 }
 
+// Optional per-phase timing: five events the caller owns, recorded on the block's stream at the start and after each of
+// the four kernels.  Thread-local, so it only affects calls of the thread that set it.
+static thread_local void* const* g_ffn_phase_events = nullptr;
+int pyc_b200_ffn_phase_events(void* const* events5) { g_ffn_phase_events = events5; return 0; }
+static inline void ffn_mark(int i, cudaStream_t s) {
+    if (g_ffn_phase_events && g_ffn_phase_events[i]) cudaEventRecord(static_cast<cudaEvent_t>(g_ffn_phase_events[i]), s);
+}
+
 static int ffn_block_impl(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* stream, const b200::Fp8Scatter* scatter) {
     if (!a || !a->x || !a->w1 || !a->w2 || !a->w1_scale || !a->w2_scale || (!a->out && !scatter) || !workspace) { set_error("ffn: NULL argument"); return -1; }
     const size_t need = pyc_b200_ffn_workspace_bytes(a->tokens, a->hidden, a->inner);
@@ -241,10 +249,15 @@ static int ffn_block_impl(const pyc_b200_ffn_args* a, void* workspace, size_t wo
     // 1. LayerNorm + per-token quantisation   2. fp8 GEMM1 (+bias) + GELU -> bf16
     // 3. per-token quantisation               4. fp8 GEMM2 (+bias) -> bf16 (a partial sum when the inner dimension is sharded;
     //                                            with `scatter`, every row goes straight to the receive slot of the rank that owns it)
+    ffn_mark(0, s);
     if (launch_rowquant<true>(a->x, a->ln_gamma, a->ln_beta, xq, xs, T, H, a->eps > 0.0f ? a->eps : 1e-5f, s) != 0) return -1;
+    ffn_mark(1, s);
     if (launch_gemm_fp8(a->tokens, a->inner, a->hidden, xq, a->w1, 0, xs, a->w1_scale, a->b1, PYC_B200_ACT_GELU, h, s, st) != 0) return -1;
+    ffn_mark(2, s);
     if (launch_rowquant<false>(h, nullptr, nullptr, hq, hs, T, I, 0.0f, s) != 0) return -1;
+    ffn_mark(3, s);
     if (launch_gemm_fp8(a->tokens, a->hidden, a->inner, hq, a->w2, 0, hs, a->w2_scale, a->b2, PYC_B200_ACT_NONE, a->out, s, st, scatter) != 0) return -1;
+    ffn_mark(4, s);
     return 0;
 }
 

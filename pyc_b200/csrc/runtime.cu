@@ -413,8 +413,15 @@ void registry_report_ms(const char* op_key, const char* symbol, double ms) {
 //      puts it more than 25 % behind the model's own best (the registry knows families, not wave quantisation);
 //      PYC_B200_REGISTRY_SELECT=0 skips this step;
 //   5. the wave-count model.
-static std::mutex g_win_mu;
-static std::map<std::tuple<int, int, int, int>, const GemmConfig*> g_winners;
+// Function-local (heap) singletons: the autotune DB is read from the load-time constructor, which can run before this
+// file's namespace-scope objects are constructed.
+struct WinnerState {
+    std::mutex mu;
+    std::map<std::tuple<int, int, int, int>, const GemmConfig*> winners;
+};
+static WinnerState& winner_state() { static WinnerState* s = new WinnerState(); return *s; }
+#define g_win_mu (winner_state().mu)
+#define g_winners (winner_state().winners)
 static std::atomic<uint64_t> g_selection_epoch{1};
 static thread_local char g_selection_source[32] = "";
 

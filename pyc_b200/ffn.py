@@ -100,7 +100,7 @@ class CollectiveBackend:
 class FfnBlock:
     """Device-resident shard of one FFN block plus its workspace; call run() once per step."""
 
-    def __init__(self, tokens, hidden, inner_local, w1, s1, w2, s2, torch, group=None, exchange="nccl", comm=None):
+    def __init__(self, tokens, hidden, inner_local, w1, s1, w2, s2, torch, group=None, exchange="nccl", comm=None, single=False):
         self.torch, self.group = torch, group
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
@@ -111,7 +111,8 @@ class FfnBlock:
         self.w2 = torch.from_numpy(np.ascontiguousarray(w2)).to(dev)
         self.s2 = torch.from_numpy(np.ascontiguousarray(s2, dtype=np.float32)).to(dev)
         dist = torch.distributed
-        self.parallel = group is not None or (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1)
+        # single=True: the whole block on this GPU even when a process group exists (no collective, no communicator)
+        self.parallel = not single and (group is not None or (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1))
         self.world = dist.get_world_size(group) if self.parallel else 1
         self.rank = dist.get_rank(group) if self.parallel else 0
         self.ws_bytes = backend.ffn_workspace_bytes(tokens, hidden, inner_local)
