@@ -915,6 +915,299 @@ attention_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Fourth kernel: two 128-query tiles per CTA, key blocks of 128, sixteen softmax warps.
+// One CTA per SM owns all 512 TMEM columns (S0 | S1 | O0 | O1); the single MMA thread alternates
+// between the tiles:
+//     P0_j V_j -> Q0 K_{j+1}^T  |  P1_j V_j -> Q1 K_{j+1}^T  |  ...
+// so that while tile 0 is in its softmax the tensor pipe works for tile 1 and vice versa, and every
+// K/V block fetched from L2 serves 256 queries.  P_j overwrites S_j in TMEM (packed 2 x 16 bit per
+// column) and is the A operand of P*V.  With a single S buffer per tile no parity can alias: Q*K^T
+// of block j+1 is issued behind P*V of block j, so when a softmax warp sees S_{j+1} the previous
+// P*V has completed.
+// Each tile has EIGHT softmax warps: a 32-lane TMEM window is shared by two warps, 16 query rows each, read with the
+// 16x256b shape (four threads per row, 32 scores per thread and row), so row maxima are two shuffles and nothing is
+// exchanged between warps.
+// Measured on B200 (256 heads x 2048 x 128): 0.509 ms non-causal / 0.330 ms causal, against 0.501 / 0.305 for the
+// 64-key kernels above, which therefore stay the default; this one is selected with PYC_B200_ATTENTION_KERNEL=4.
+// A cycle-stamp timeline of its main loop shows a period of ~3300 cycles per key block for 2048 cycles of tensor work:
+// each tile's chain Q*K^T (560) -> scores seen (110) -> TMEM load (70) -> softmax (1750) -> store, hand-over (350) ->
+// P*V (480) is serial because a tile has one S buffer, and the softmax itself runs at ~60 % of the rate the same
+// instruction mix reaches alone (a micro-benchmark of ex2 + fma.f32x2 + add.f32x2 + cvt.bf16x2 + max runs at the
+// special-function unit's 8 cycles per warp instruction).  One warp per window (32x32b shape), handing P over in two
+// halves, and one issuing thread per tile were measured too: equal, equal and 30 % slower.
+// ---------------------------------------------------------------------------------------
+template <int HD>
+struct AttnSmem4 {
+    static constexpr int TILE = 128 * HD * 2;          // one [128 x HD] 16-bit tile (a Q tile, a K block or a V block)
+    static constexpr int Q_OFF = 0, K_OFF = 2 * TILE, V_OFF = 4 * TILE, BAR_OFF = 6 * TILE;
+    static constexpr int NUM_BARS = 16;
+    static constexpr size_t BYTES = 1024 + BAR_OFF + NUM_BARS * 8 + 16;
+};
+
+constexpr int ATTN4_THREADS = 18 * 32;   // 16 softmax warps, MMA warp, TMA warp
+
+template <int HD, int FMT, int POLY>
+__global__ void __launch_bounds__(ATTN4_THREADS, 1)
+attention_tc4_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, AttnParams ap, int* status) {
+    using SM = AttnSmem4<HD>;
+    using E = AElem<FMT>;
+    using T = typename E::T;
+    constexpr int BK = 128;                          // keys per block
+    constexpr int HALVES = HD / 64;
+    constexpr int SLAB = 128 * 128;                  // [128 rows x 128 B]
+    constexpr uint32_t IDESC_QK = make_idesc(FMT, FMT, 0, 0, BQ, BK);
+    constexpr uint32_t IDESC_PV = make_idesc(FMT, FMT, 0, 1, BQ, HD);
+    constexpr uint32_t TMEM_COLS = 512;              // S0 @0, S1 @128, O0 @256, O1 @256 + HD
+    constexpr uint32_t O_COL = 256;
+    constexpr int MMA_WARP = 16, TMA_WARP = 17;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + SM::NUM_BARS);
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 24, v_full = bar0 + 40, v_empty = bar0 + 56,
+                   s_full = bar0 + 72, p_full = bar0 + 88, pv_done = bar0 + 104;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_pairs = (ap.seq + 2 * BQ - 1) / (2 * BQ);
+    const int pair = num_pairs - 1 - static_cast<int>(blockIdx.x);   // longest (causal) work first
+    const int bh = blockIdx.y;
+    const int q_base = pair * 2 * BQ;
+    const int kv_all = (ap.seq + BK - 1) / BK;
+    int nblk[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int q0t = q_base + t * BQ;
+        nblk[t] = q0t >= ap.seq ? 0 : (ap.causal ? min(kv_all, q0t / BK + 1) : kv_all);
+    }
+    const int n_loop = max(nblk[0], nblk[1]);
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full + 8 * i, 1); mbar_init(k_empty + 8 * i, 1);
+            mbar_init(v_full + 8 * i, 1); mbar_init(v_empty + 8 * i, 1);
+            mbar_init(s_full + 8 * i, 1); mbar_init(p_full + 8 * i, 8); mbar_init(pv_done + 8 * i, 1);
+        }
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == MMA_WARP) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    const uint32_t sQ = smem_u32(smem + SM::Q_OFF), sK = smem_u32(smem + SM::K_OFF), sV = smem_u32(smem + SM::V_OFF);
+
+    if (warp == TMA_WARP) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, 2 * SM::TILE);
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) tma_load_3d(sQ + t * SM::TILE + h * SLAB, &tmQ, q_full, h * 64, q_base + t * BQ, bh);
+            for (int j = 0; j < n_loop; ++j) {
+                const int st = j & 1;
+                const uint32_t par = ((j >> 1) & 1) ^ 1;
+                if (!mbar_wait(k_empty + 8 * st, par, status, 0x71)) break;
+                mbar_arrive_expect_tx(k_full + 8 * st, SM::TILE);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) tma_load_3d(sK + st * SM::TILE + h * SLAB, &tmK, k_full + 8 * st, h * 64, j * BK, bh);
+                if (!mbar_wait(v_empty + 8 * st, par, status, 0x72)) break;
+                mbar_arrive_expect_tx(v_full + 8 * st, SM::TILE);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) tma_load_3d(sV + st * SM::TILE + h * SLAB, &tmV, v_full + 8 * st, h * 64, j * BK, bh);
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        if (lane == 0) {
+            constexpr uint32_t HI = smem_desc_hi_sw128(1024);
+            const uint32_t q_lo0 = smem_desc_lo(sQ, 16), k_lo0 = smem_desc_lo(sK, 16), v_lo0 = smem_desc_lo(sV, SLAB);
+            auto issue_qk = [&](int t, int j) {   // S_t = Q_t K_j^T, 128 x 128 x HD
+                const uint32_t d = tmem_base + t * BK;
+                const uint32_t q_lo = q_lo0 + t * (SM::TILE >> 4), k_lo = k_lo0 + (j & 1) * (SM::TILE >> 4);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t off = ((ks / 4) * SLAB + (ks % 4) * 32) >> 4;
+                    umma_f16(d, smem_desc_join(q_lo + off, HI), smem_desc_join(k_lo + off, HI), IDESC_QK, ks != 0);
+                }
+                umma_commit(s_full + 8 * t);
+            };
+            auto issue_pv = [&](int t, int j) {   // O_t += P_t V_j, 128 x HD x 128, A from TMEM (8 columns per 16 keys)
+                const uint32_t p_tmem = tmem_base + t * BK, o = tmem_base + O_COL + t * HD;
+                const uint32_t v_lo = v_lo0 + (j & 1) * (SM::TILE >> 4);
+#pragma unroll
+                for (int ks = 0; ks < BK / 16; ++ks)
+                    umma_f16_ts(o, p_tmem + ks * 8, smem_desc_join(v_lo + ks * (2048 >> 4), HI), IDESC_PV, (j | ks) != 0 ? 1u : 0u);
+                umma_commit(pv_done + 8 * t);
+            };
+            bool ok = mbar_wait(q_full, 0, status, 0x73) && mbar_wait(k_full, 0, status, 0x74);
+            if (ok) {
+                tc_fence_after();
+                if (nblk[0] > 0) issue_qk(0, 0);
+                if (nblk[1] > 0) issue_qk(1, 0);
+                umma_commit(k_empty);
+            }
+            for (int j = 0; j < n_loop && ok; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(v_full + 8 * st, (j >> 1) & 1, status, 0x75)) { ok = false; break; }
+                bool k_next = false;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (j >= nblk[t]) continue;
+                    if (!mbar_wait(p_full + 8 * t, j & 1, status, 0x76)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_pv(t, j);
+                    if (j + 1 < nblk[t]) {
+                        if (!k_next) {
+                            if (!mbar_wait(k_full + 8 * ((j + 1) & 1), ((j + 1) >> 1) & 1, status, 0x77)) { ok = false; break; }
+                            tc_fence_after();
+                            k_next = true;
+                        }
+                        issue_qk(t, j + 1);
+                    }
+                }
+                if (!ok) break;
+                umma_commit(v_empty + 8 * st);
+                if (j + 1 < n_loop) umma_commit(k_empty + 8 * ((j + 1) & 1));
+            }
+        }
+    } else {
+        // Softmax warps.  Warp w: tile t = w / 8, TMEM lane window 32 * (w % 4), rows 16 * ((w / 4) % 2) .. + 15 of it.
+        // Thread 4*i + c of the warp: rows i ("A") and i + 8 ("B") of those sixteen, score columns 8k + 2c, 8k + 2c + 1.
+        const int t = warp >> 3;
+        const int row16 = (warp & 3) * 32 + ((warp >> 2) & 1) * 16;      // first of this warp's 16 query rows inside the tile
+        const int c2 = (lane & 3) * 2;
+        const int q0 = q_base + t * BQ;
+        const int qa = q0 + row16 + (lane >> 2), qb = qa + 8;            // the thread's two query rows (global index)
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(row16) << 16);
+        const uint32_t s_addr = lane_addr + t * BK, o_addr = lane_addr + O_COL + t * HD;
+        const int my_blocks = nblk[t];
+        float m_a = -INFINITY, m_b = -INFINITY;
+        unsigned long long l_ab = 0ull;          // this thread's share of the two row sums
+        bool ok = true;
+        int lim_a = ap.seq, lim_b = ap.seq;
+        if (ap.causal) { lim_a = min(lim_a, qa + 1); lim_b = min(lim_b, qb + 1); }
+        const unsigned long long sc2 = f32x2_splat(ap.scale_log2);
+        for (int j = 0; j < my_blocks && ok; ++j) {
+            if (!mbar_wait(s_full + 8 * t, j & 1, status, 0x78)) { ok = false; break; }
+            tc_fence_after();
+            const int k0 = j * BK;
+            uint32_t r[64];
+            tmem_ld_16x256b_x16(s_addr, r);
+            tmem_ld_wait();
+            // only blocks that touch the diagonal or the end of the sequence need per-element masking (warp-uniform test)
+            const bool masked = (k0 + BK > ap.seq) || (ap.causal && k0 + BK > q0 + row16 + 1);
+            if (masked) {
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    const int key = k0 + 8 * k + c2;
+                    if (key >= lim_a) r[4 * k] = 0xff800000u;        // -inf
+                    if (key + 1 >= lim_a) r[4 * k + 1] = 0xff800000u;
+                    if (key >= lim_b) r[4 * k + 2] = 0xff800000u;
+                    if (key + 1 >= lim_b) r[4 * k + 3] = 0xff800000u;
+                }
+            }
+            float mx_a = -INFINITY, mx_b = -INFINITY;
+            {
+                float ma[2] = {-INFINITY, -INFINITY}, mb[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    ma[k & 1] = fmax3(ma[k & 1], __uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]));
+                    mb[k & 1] = fmax3(mb[k & 1], __uint_as_float(r[4 * k + 2]), __uint_as_float(r[4 * k + 3]));
+                }
+                mx_a = fmaxf(ma[0], ma[1]); mx_b = fmaxf(mb[0], mb[1]);
+                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+            }
+            mx_a *= ap.scale_log2; mx_b *= ap.scale_log2;
+            // Lazy rescale: a row's reference maximum only moves when the new block exceeds it by more than 2^8.
+            const float na = fmaxf(m_a, mx_a), nb = fmaxf(m_b, mx_b);
+            const bool move_a = na > m_a + 8.0f || m_a == -INFINITY, move_b = nb > m_b + 8.0f || m_b == -INFINITY;
+            const float ra = move_a ? na : m_a, rb = move_b ? nb : m_b;
+            const float ua = ra == -INFINITY ? 0.0f : ra, ub = rb == -INFINITY ? 0.0f : rb;
+            const float alpha_a = move_a ? fast_exp2(m_a - ua) : 1.0f, alpha_b = move_b ? fast_exp2(m_b - ub) : 1.0f;   // m = -inf -> 0
+            m_a = ra; m_b = rb;
+            const unsigned long long mu_a = f32x2_splat(-ua), mu_b = f32x2_splat(-ub);
+            l_ab = f32x2_mul(l_ab, f32x2_pack(alpha_a, alpha_b));
+            if (j > 0 && __any_sync(0xffffffffu, move_a || move_b)) {
+                // O_t is only touched when some row of this warp moved its reference maximum.  P*V of block j-1 has completed
+                // (Q*K^T of this block was issued behind it); the wait is immediate and orders the TMEM accesses.
+                if (!mbar_wait(pv_done + 8 * t, (j - 1) & 1, status, 0x79)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll 1
+                for (int cc = 0; cc < HD / 32; ++cc) {      // 32 columns at a time: the scores stay in registers meanwhile
+                    uint32_t o[16];
+                    tmem_ld_16x256b_x4(o_addr + cc * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        o[4 * k] = __float_as_uint(__uint_as_float(o[4 * k]) * alpha_a); o[4 * k + 1] = __float_as_uint(__uint_as_float(o[4 * k + 1]) * alpha_a);
+                        o[4 * k + 2] = __float_as_uint(__uint_as_float(o[4 * k + 2]) * alpha_b); o[4 * k + 3] = __float_as_uint(__uint_as_float(o[4 * k + 3]) * alpha_b);
+                    }
+                    tmem_st_16x256b_x4(o_addr + cc * 32, o);
+                }
+            }
+            // exponent arguments two lanes per instruction, one special-function op per exponential
+            unsigned long long la = 0ull, lb = 0ull;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                float xa0, xa1, xb0, xb1;
+                f32x2_unpack(f32x2_fma(f32x2_pack(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1])), sc2, mu_a), xa0, xa1);
+                f32x2_unpack(f32x2_fma(f32x2_pack(__uint_as_float(r[4 * k + 2]), __uint_as_float(r[4 * k + 3])), sc2, mu_b), xb0, xb1);
+                const float a0 = fast_exp2(xa0), b0 = fast_exp2(xb0);
+                const float a1 = (POLY >= 1 && (k & 1)) || POLY >= 2 ? poly_exp2(xa1) : fast_exp2(xa1);
+                const float b1 = (POLY >= 1 && (k & 1)) || POLY >= 2 ? poly_exp2(xb1) : fast_exp2(xb1);
+                la = f32x2_add(la, f32x2_pack(a0, a1));
+                lb = f32x2_add(lb, f32x2_pack(b0, b1));
+                r[4 * k] = E::pack(a0, a1);          // packed in place: even elements are the 16x128b store's registers
+                r[4 * k + 2] = E::pack(b0, b1);
+            }
+            tmem_st_16x128b_x16_even(s_addr, r);
+            {
+                float a_lo, a_hi, b_lo, b_hi;
+                f32x2_unpack(la, a_lo, a_hi); f32x2_unpack(lb, b_lo, b_hi);
+                l_ab = f32x2_add(l_ab, f32x2_pack(a_lo + a_hi, b_lo + b_hi));
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full + 8 * t);
+        }
+        if (ok && my_blocks > 0 && mbar_wait(pv_done + 8 * t, (my_blocks - 1) & 1, status, 0x7a)) {
+            tc_fence_after();
+            float l_a, l_b;
+            f32x2_unpack(l_ab, l_a, l_b);
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 2); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+            const float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
+            uint32_t o[HD / 2];
+            if constexpr (HD == 128) tmem_ld_16x256b_x16(o_addr, o); else tmem_ld_16x256b_x8(o_addr, o);
+            tmem_ld_wait();
+            T* out = reinterpret_cast<T*>(ap.out) + static_cast<size_t>(bh) * ap.seq * HD;
+            uint32_t* row_a = reinterpret_cast<uint32_t*>(out + static_cast<size_t>(qa) * HD + c2);
+            uint32_t* row_b = reinterpret_cast<uint32_t*>(out + static_cast<size_t>(qb) * HD + c2);
+#pragma unroll
+            for (int k = 0; k < HD / 8; ++k) {       // columns 8k + 2c, + 1: one 4-byte store per row and k
+                if (qa < ap.seq) row_a[4 * k] = E::pack(__uint_as_float(o[4 * k]) * inv_a, __uint_as_float(o[4 * k + 1]) * inv_a);
+                if (qb < ap.seq) row_b[4 * k] = E::pack(__uint_as_float(o[4 * k + 2]) * inv_b, __uint_as_float(o[4 * k + 3]) * inv_b);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        if (*reinterpret_cast<volatile int*>(status) != ST_OK) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
 // Any-shape path (fp32, head sizes other than 64/128, unaligned pointers): one warp per
 // query row, online softmax over the keys, lanes split the head dimension.
 __device__ __forceinline__ float ald(const float* p) { return __ldg(p); }
@@ -979,6 +1272,7 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
     // the second made persistent.
     const char* pick = getenv("PYC_B200_ATTENTION_KERNEL");
     const bool first = pick && pick[0] == '1';
+    const bool fourth = pick && pick[0] == '4';
     // Without a choice from the environment: causal work up to 4096 keys (query blocks of very different length, many short
     // ones) goes to the persistent kernel, 2-13 % faster there; long or non-causal work, where every CTA runs the same long
     // loop, is 2-5 % faster with one CTA per query block (measured at 2048, 4096 and 8192 keys).
@@ -989,13 +1283,28 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
     const uint64_t dims[3] = {static_cast<uint64_t>(HD), static_cast<uint64_t>(seq), static_cast<uint64_t>(bh)};
     const uint64_t str[2] = {static_cast<uint64_t>(HD) * 2, static_cast<uint64_t>(seq) * HD * 2};
     const uint32_t box_q[3] = {64, 128, 1};
-    const uint32_t box_kv[3] = {64, static_cast<uint32_t>(first ? BKV : BKV2), 1};
+    const uint32_t box_kv[3] = {64, static_cast<uint32_t>(first || fourth ? BKV : BKV2), 1};
     if (encode_tmap(&tq, q, 2, 3, dims, str, box_q, true) != 0 || encode_tmap(&tk, k, 2, 3, dims, str, box_kv, true) != 0 ||
         encode_tmap(&tv, v, 2, 3, dims, str, box_kv, true) != 0) return -1;
     AttnParams ap;
     ap.seq = seq; ap.batch_heads = bh; ap.causal = causal ? 1 : 0; ap.scale_log2 = scale * 1.4426950408889634f; ap.out = out;
     dim3 grid((seq + BQ - 1) / BQ, bh);
-    if (first) {
+    if (fourth) {
+        const char* pe = getenv("PYC_B200_ATTENTION_POLY");
+        const int poly = pe && pe[0] >= '0' && pe[0] <= '2' ? pe[0] - '0' : 0;
+        constexpr size_t smem = AttnSmem4<HD>::BYTES > 120 * 1024 ? AttnSmem4<HD>::BYTES : 120 * 1024;   // one CTA per SM: it takes all 512 TMEM columns
+        static bool attr_set4[16][3] = {};
+        auto k0 = attention_tc4_kernel<HD, FMT, 0>;
+        auto k1 = attention_tc4_kernel<HD, FMT, 1>;
+        auto k2 = attention_tc4_kernel<HD, FMT, 2>;
+        auto kernel = poly == 0 ? k0 : poly == 1 ? k1 : k2;
+        if (dev < 16 && !attr_set4[dev][poly]) {
+            B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            attr_set4[dev][poly] = true;
+        }
+        dim3 grid4((seq + 2 * BQ - 1) / (2 * BQ), bh);
+        kernel<<<grid4, ATTN4_THREADS, smem, stream>>>(tq, tk, tv, ap, status);
+    } else if (first) {
         auto kernel = attention_tc_kernel<HD, FMT>;
         // At least 120 KB so that two CTAs never share an SM: each one takes all 512 TMEM columns.
         constexpr size_t smem = AttnSmem<HD>::BYTES > 120 * 1024 ? AttnSmem<HD>::BYTES : 120 * 1024;

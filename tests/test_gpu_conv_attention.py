@@ -88,7 +88,7 @@ def attn_case(backend, oracle_lib, dtype, bh, seq, d, causal, seed=0, symbol=Non
     assert err <= (tol or TOL[dtype]), f"attention bh={bh} seq={seq} d={d} causal={causal}: rel err {err:.3e}"
 
 
-@pytest.fixture(params=["1", "2", "3"], ids=["kernel1_smemP", "kernel2_tmemP", "kernel3_persistent"])
+@pytest.fixture(params=["1", "2", "3", "4"], ids=["kernel1_smemP", "kernel2_tmemP", "kernel3_persistent", "kernel4_two_tiles"])
 def attn_kernel(request, monkeypatch):
     # all tensor-core kernels are held to the same bar; the env switch picks one
     monkeypatch.setenv("PYC_B200_ATTENTION_KERNEL", request.param)
