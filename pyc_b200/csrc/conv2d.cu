@@ -19,6 +19,7 @@
 // C % 8 == 0 take this path; anything else runs the direct kernel below.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "internal.h"
@@ -54,8 +55,8 @@ template <> struct CElem<0> {
     static __device__ __forceinline__ uint32_t pack(float a, float b) { __half2 p = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&p); }
 };
 
-template <int BN, int STAGES, int FMT>
-__global__ void __launch_bounds__(192, 1)
+template <int BN, int STAGES, int FMT, int CTAS_PER_SM>
+__global__ void __launch_bounds__(192, CTAS_PER_SM)
 conv2d_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW, ConvParams cp, int* status) {
     constexpr int B_STAGE_BYTES = BN * BK * 2;
     constexpr uint32_t STAGE_TX = A_STAGE_BYTES + B_STAGE_BYTES;
@@ -264,9 +265,9 @@ conv2d_direct_kernel(const T* __restrict__ in, const T* __restrict__ w, const T*
 template <int BN, int STAGES>
 constexpr size_t conv_smem_bytes() { return 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16; }
 
-template <int BN, int STAGES, int FMT>
+template <int BN, int STAGES, int FMT, int CTAS_PER_SM = 1>
 int launch_conv_tc(const CUtensorMap& tmIn, const CUtensorMap& tmW, const ConvParams& cp, cudaStream_t stream, int* status) {
-    auto kernel = conv2d_tc_kernel<BN, STAGES, FMT>;
+    auto kernel = conv2d_tc_kernel<BN, STAGES, FMT, CTAS_PER_SM>;
     constexpr size_t smem = conv_smem_bytes<BN, STAGES>();
     static bool attr_set[16] = {};
     int dev = 0;
@@ -276,7 +277,8 @@ int launch_conv_tc(const CUtensorMap& tmIn, const CUtensorMap& tmW, const ConvPa
         attr_set[dev] = true;
     }
     const int tiles = cp.tiles_q * cp.tiles_p * cp.tiles_n_img * cp.tiles_k;
-    kernel<<<tiles < sm_count() ? tiles : sm_count(), 192, smem, stream>>>(tmIn, tmW, cp, status);
+    const int slots = sm_count() * CTAS_PER_SM;
+    kernel<<<tiles < slots ? tiles : slots, 192, smem, stream>>>(tmIn, tmW, cp, status);
     B200_CUDA_OK(cudaGetLastError());
     count_launch();
     return 0;
@@ -315,8 +317,8 @@ int launch_conv2d(pyc_dtype dt, int N, int H, int W, int C, int K, int R, int S,
             default: set_error("conv2d: unsupported dtype %d", static_cast<int>(dt)); return -1;
         }
     }
-    // Brick of 128 output pixels: powers of two tq*tp*tn == 128 with the least padding waste; ties go to the widest row run.
     ConvParams cp;
+    // Brick of 128 output pixels: powers of two tq*tp*tn == 128 with the least padding waste; ties go to the widest row run.
     double best = -1.0;
     for (int tq = 128; tq >= 1; tq >>= 1)
         for (int tp = 128 / tq; tp >= 1; tp >>= 1) {
@@ -341,7 +343,11 @@ int launch_conv2d(pyc_dtype dt, int N, int H, int W, int C, int K, int R, int S,
     if (encode_tmap(&tmW, filt, 2, 3, w_dims, w_str, w_box, true) != 0) return -1;
 
     const bool bf16 = dt == PYC_DTYPE_BF16;
-    if (bn == 64) return bf16 ? launch_conv_tc<64, 8, 1>(tmIn, tmW, cp, stream, status) : launch_conv_tc<64, 8, 0>(tmIn, tmW, cp, stream, status);
+    // 64 filters: two CTAs per SM (4-stage rings, 128 TMEM columns each).  With N = 64 an MMA reads 6 KB of operands from
+    // shared memory for 32 cycles of math, and a cycle-stamp timeline shows ~83 cycles per 128x64x16 MMA: the kernel is bound
+    // by the operand reads, not by its loads (a variant that fetched each input brick once with its halo, a third of the
+    // L2 traffic, ran at the same 30 us on 64 x 56 x 56 x 64) -- the second CTA fills the gaps between tiles: 36 -> 31 us.
+    if (bn == 64) return bf16 ? launch_conv_tc<64, 4, 1, 2>(tmIn, tmW, cp, stream, status) : launch_conv_tc<64, 4, 0, 2>(tmIn, tmW, cp, stream, status);
     if (bn == 128) return bf16 ? launch_conv_tc<128, 6, 1>(tmIn, tmW, cp, stream, status) : launch_conv_tc<128, 6, 0>(tmIn, tmW, cp, stream, status);
     return bf16 ? launch_conv_tc<256, 4, 1>(tmIn, tmW, cp, stream, status) : launch_conv_tc<256, 4, 0>(tmIn, tmW, cp, stream, status);
 }

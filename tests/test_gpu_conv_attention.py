@@ -45,6 +45,17 @@ def test_conv_tc_filter_shapes_and_f16(backend, oracle_lib):
     conv_case(backend, oracle_lib, abi.DTYPE_F16, 4, 14, 14, 128, 64, seed=4)
 
 
+def test_conv_64_filters_two_ctas_per_sm(backend, oracle_lib):
+    # K <= 64 runs two co-resident CTAs per SM: ragged P/Q, 1 x 1 and 3 x 2 filters, fewer than 64 filters, no padding, f16,
+    # and more bricks than CTA slots
+    conv_case(backend, oracle_lib, abi.DTYPE_BF16, 3, 19, 21, 64, 64, seed=31)
+    conv_case(backend, oracle_lib, abi.DTYPE_BF16, 2, 56, 56, 64, 64, seed=32)
+    conv_case(backend, oracle_lib, abi.DTYPE_BF16, 2, 17, 9, 64, 40, R=3, S=2, pad=(1, 0), seed=33)
+    conv_case(backend, oracle_lib, abi.DTYPE_BF16, 2, 12, 12, 64, 64, R=1, S=1, pad=(0, 0), bias=False, relu=False, seed=34)
+    conv_case(backend, oracle_lib, abi.DTYPE_F16, 2, 30, 8, 64, 64, R=3, S=3, pad=(0, 0), seed=35)
+    conv_case(backend, oracle_lib, abi.DTYPE_BF16, 150, 8, 16, 64, 64, seed=36)                  # more bricks than SMs: CTAs loop
+
+
 def test_conv_direct_paths_and_legacy_symbols(backend, oracle_lib):
     conv_case(backend, oracle_lib, abi.DTYPE_BF16, 2, 15, 15, 64, 32, stride=(2, 2), seed=5)      # stride 2
     conv_case(backend, oracle_lib, abi.DTYPE_BF16, 2, 9, 9, 12, 20, seed=6)                        # C % 8 != 0
