@@ -458,8 +458,13 @@ class Extras:
             one = {"ms": mean, "tflops": tf, "frac": tf / self.burst, "frac_fp8": tf / (2 * self.burst),
                    "max_rel_err_vs_oracle_sample": self.rel_err(self.f32(blk.out[rows]), want)}
             one.update(phases(run))
+            replay = blk.capture(self.bits(x))
+            g_mean, _ = self.time_launch(replay, iters=10, flush=False)
+            one["ms_graph_replay"] = g_mean
+            one["max_rel_err_graph_replay"] = self.rel_err(self.f32(blk.out[rows]), want)
             res["one_gpu"] = one
-            del blk
+            blk.close()
+            del blk, replay
         if world > 1:
             self.host_barrier()
             comm = ffn.CollectiveBackend(torch)
@@ -488,8 +493,21 @@ class Extras:
                 dist.all_reduce(pt, op=dist.ReduceOp.MAX)
                 entry["phases_max_over_ranks"] = dict(zip(ph.keys(), pt.tolist()))
                 entry["exchange_ms"] = ms - float(pt.sum())      # everything of a step that is not one of the four kernels
+                replay = blk.capture(self.bits(x))
+                for _ in range(3):
+                    replay()
+                torch.cuda.synchronize(); dist.barrier()
+                e0.record()
+                for _ in range(iters):
+                    out = replay()
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / iters, self.rel_err(self.f32(out[rows]), want)], dtype=torch.float64, device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                entry["ms_graph_replay"], entry["max_rel_err_graph_replay"] = float(t[0]), float(t[1])
                 tp[exchange] = entry
                 dist.barrier()
+                del replay
                 blk.close()
             # the 67 MB bf16 all-reduce alone, through the same vtable
             buf = torch.zeros((tokens, hidden), dtype=torch.bfloat16, device="cuda")
@@ -510,7 +528,8 @@ class Extras:
             tp["all_reduce_alone"] = {"ms": float(t[0]), "bytes": nbytes, "bus_gbs": 2.0 * (world - 1) / world * nbytes / (float(t[0]) * 1e-3) / 1e9}
             tp["world"] = world
             tp["max_rel_err"] = max(tp["nccl"]["max_rel_err"], tp["peer"]["max_rel_err"])
-            tp["ms"] = min(tp["nccl"]["ms"], tp["peer"]["ms"])
+            tp["ms"] = min(tp[e][k] for e in ("nccl", "peer") for k in ("ms", "ms_graph_replay"))
+            tp["max_rel_err"] = max(tp["max_rel_err"], tp["nccl"]["max_rel_err_graph_replay"], tp["peer"]["max_rel_err_graph_replay"])
             comm.close()
             res_tp = tp
             self.out["ffn_tp"] = res_tp

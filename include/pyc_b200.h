@@ -323,6 +323,13 @@ int pyc_b200_set_stream(void* stream, int async);
  * (site << 8) | 1, or -1 if no device. */
 int pyc_b200_device_status(void);
 
+/* Self-test of the bounded waits: enqueue on `stream` a one-CTA kernel that waits, for at most about limit_us
+ * microseconds (1 .. 1000000), on a barrier nobody arrives at.  The wait runs out by itself, the kernel records
+ * (0x7f << 8) | 1 in the device status word and returns; pyc_b200_device_status() then reports that value once, and a
+ * pyc_cuda_dispatch that runs before the word has been read returns PYC_CUDA_DISPATCH_ERROR with the reason
+ * "b200_kernel_wait_timeout:0x7f01".  Nothing hangs, traps or faults.  Returns 0 / -1. */
+int pyc_b200_selftest_wait_timeout(int limit_us, void* stream);
+
 /* Last error text of the calling thread ("" when none). */
 const char* pyc_b200_last_error(void);
 

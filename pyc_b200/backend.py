@@ -23,7 +23,7 @@ EXPORTS = [
     "pyc_b200_reduce_sum", "pyc_b200_quantize_rows", "pyc_b200_layernorm_quantize", "pyc_b200_gemm_fp8",
     "pyc_b200_ffn_workspace_bytes", "pyc_b200_ffn_block", "pyc_b200_ffn_block_tp", "pyc_b200_ffn_phase_events", "pyc_b200_ffn_block_scatter", "pyc_b200_tp_reduce_broadcast",
     "pyc_b200_symm_alloc", "pyc_b200_symm_open", "pyc_b200_symm_close", "pyc_b200_symm_free", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm", "pyc_b200_autotune_db_load", "pyc_b200_last_plan", "pyc_b200_plan_arena",
-    "pyc_b200_get_runtime_info", "pyc_b200_set_stream", "pyc_b200_device_status", "pyc_b200_last_error",
+    "pyc_b200_get_runtime_info", "pyc_b200_set_stream", "pyc_b200_device_status", "pyc_b200_selftest_wait_timeout", "pyc_b200_last_error",
     "pyc_b200_shutdown",
 ]
 
@@ -319,6 +319,10 @@ def kernel_count(op_key):
 
 def set_stream(stream, async_=False):
     _check(load().pyc_b200_set_stream(stream, int(async_)), "pyc_b200_set_stream")
+
+
+def selftest_wait_timeout(limit_us=50, stream=0):
+    _check(load().pyc_b200_selftest_wait_timeout(limit_us, stream), "pyc_b200_selftest_wait_timeout")
 
 
 def device_status():

@@ -16,6 +16,7 @@
 //   * tensors may be device pointers (zero copy) or host pointers (pinned
 //     staging, as PyC does at cuda_backend.c:1766-1853).
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -88,11 +89,13 @@ struct Value {
     int consumers = 0;
 };
 
-enum StepKind { S_H2D = 0, S_GEMM, S_ADD, S_BIAS_ACT, S_LAYERNORM, S_REDUCE_SUM, S_COPY, S_D2H };
+enum StepKind { S_H2D = 0, S_GEMM, S_ADD, S_BIAS_ACT, S_LAYERNORM, S_REDUCE_SUM, S_COPY, S_D2H, S_SOFTMAX, S_ATTENTION, S_CONV2D, S_FFN_FP8 };
 struct Step {
     StepKind kind;
     int out = -1;            // value id written (temps) or -1
-    int in0 = -1, in1 = -1, in2 = -1;
+    int in0 = -1, in1 = -1, in2 = -1, in3 = -1, in4 = -1;
+    int scratch = -1;        // value id of a step-private workspace in the arena (extended ops)
+    int xp[12] = {0};        // parameters of an extended op (see parse_extended_op)
     int ext = -1;            // inputs[]/outputs[] index for copies
     int add_mode = 0, act = 0;
     size_t rows = 0, cols = 0, bytes = 0;
@@ -128,6 +131,37 @@ uint64_t fnv1a(uint64_t h, const void* data, size_t n) {
     return h;
 }
 
+// ---- ops PyC's IR cannot name: the side table is the op NAME ---------------------------------------------------------
+// PyC's op kinds stop at matmul / add / relu / gelu / reduce_sum / layernorm (include/pyc/ir.h:16-40) and its ops carry no
+// attributes.  Without touching a PyC header, an op of kind REDUCE_SUM (the one kind whose declared shape PyC's shape
+// inference leaves alone, src/compiler/passes/pass_manager.c:171-203) whose NAME starts with "b200." is read as:
+//   b200.softmax                        softmax over the last axis of input 0
+//   b200.attention[.causal]             inputs Q, K, V of shape [..., S, D]: softmax(Q K^T / sqrt(D)) V per leading index
+//   b200.conv2d.p<ph>x<pw>.s<sh>x<sw>[.relu]   inputs X [N,H,W,C], W [K,R,S,C] and optionally bias [K]; NHWC forward convolution
+//   b200.ffn_fp8                        inputs x [T,H] bf16, W1 [H,I] and W2 [I,H] as I8 (e4m3 codes), s1 [I], s2 [H] f32:
+//                                       gelu(layernorm(x) W1) W2 with per-token activation quantisation (bf16 out)
+// The op's declared shape is its output shape.  Names survive PyC's compile step unchanged and are part of its module
+// fingerprint, so PyC's caches tell such modules apart.  PyC's CPU executor does not know these ops (it rejects REDUCE_SUM):
+// such a module has no CPU fallback, by construction.
+enum ExtOp { EXT_NONE = 0, EXT_SOFTMAX, EXT_ATTENTION, EXT_CONV2D, EXT_FFN_FP8, EXT_BAD };
+ExtOp parse_extended_op(const char* name, int* xp) {
+    if (strncmp(name, "b200.", 5) != 0) return EXT_NONE;
+    const char* r = name + 5;
+    if (!strcmp(r, "softmax")) return EXT_SOFTMAX;
+    if (!strcmp(r, "attention")) { xp[0] = 0; return EXT_ATTENTION; }
+    if (!strcmp(r, "attention.causal")) { xp[0] = 1; return EXT_ATTENTION; }
+    if (!strcmp(r, "ffn_fp8")) return EXT_FFN_FP8;
+    if (!strncmp(r, "conv2d.", 7)) {
+        int ph = 0, pw = 0, sh = 1, sw = 1, used = 0;
+        if (sscanf(r + 7, "p%dx%d.s%dx%d%n", &ph, &pw, &sh, &sw, &used) != 4) return EXT_BAD;
+        const char* tail = r + 7 + used;
+        if (tail[0] && strcmp(tail, ".relu") != 0) return EXT_BAD;
+        xp[0] = ph; xp[1] = pw; xp[2] = sh; xp[3] = sw; xp[4] = tail[0] ? 1 : 0;
+        return EXT_CONV2D;
+    }
+    return EXT_BAD;
+}
+
 // Build the step list.  Returns 0, 1 (module uses something the GPU path does not
 // know: caller falls back) or -1 (malformed call).
 int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, pyc_tensor* outputs, size_t n_out,
@@ -136,6 +170,7 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
     const size_t n = m->op_count;
     std::vector<Value>& V = plan->values;
     V.assign(n, Value());
+    V.reserve(n + 64);        // step-private workspaces are appended behind the ops' values without moving them
     size_t in_i = 0, out_i = 0;
 
     // Pass 1: shapes, dtypes, consumer counts.
@@ -178,6 +213,16 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
             case PYC_IR_OP_REDUCE_SUM: {
                 if (op.input_count < 1) return -1;
                 const Value& a = V[op.input_ids[0]];
+                int xp[12] = {0};
+                const ExtOp ext = parse_extended_op(op.name, xp);
+                if (ext == EXT_BAD) return 1;
+                if (ext != EXT_NONE) {
+                    if (ext == EXT_SOFTMAX && !op.shape.rank) { copy_shape(a); break; }
+                    if (!op.shape.rank) return -1;          // the declared shape IS the output shape
+                    v.rank = op.shape.rank; memcpy(v.dims, op.shape.dims, sizeof(v.dims));
+                    v.dtype = ext == EXT_FFN_FP8 ? PYC_DTYPE_BF16 : a.dtype;
+                    break;
+                }
                 if (op.shape.rank) { v.rank = op.shape.rank; memcpy(v.dims, op.shape.dims, sizeof(v.dims)); }
                 else if (a.rank > 1) { v.rank = a.rank - 1; memcpy(v.dims, a.dims, sizeof(v.dims)); v.dims[a.rank - 1] = 0; }
                 else { v.rank = 1; v.dims[0] = 1; }
@@ -298,6 +343,52 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
             }
             case PYC_IR_OP_REDUCE_SUM: {
                 const Value& a = V[op.input_ids[0]];
+                Step xs;
+                const ExtOp ext = parse_extended_op(op.name, xs.xp);
+                if (ext != EXT_NONE) {
+                    xs.op_main = static_cast<int>(i); xs.out = static_cast<int>(i); V[i].kind = V_TEMP;
+                    xs.in0 = op.input_ids[0];
+                    xs.in1 = op.input_count > 1 ? op.input_ids[1] : -1; xs.in2 = op.input_count > 2 ? op.input_ids[2] : -1;
+                    xs.in3 = op.input_count > 3 ? op.input_ids[3] : -1; xs.in4 = op.input_count > 4 ? op.input_ids[4] : -1;
+                    const Value& o = V[i];
+                    if (ext == EXT_SOFTMAX) {
+                        if (o.elems != a.elems || a.rank < 1) return 1;
+                        xs.kind = S_SOFTMAX; xs.cols = static_cast<size_t>(a.dims[a.rank - 1]); xs.rows = a.elems / xs.cols;
+                    } else if (ext == EXT_ATTENTION) {
+                        if (op.input_count < 3 || a.rank < 2) return -1;
+                        const Value &kk = V[xs.in1], &vv = V[xs.in2];
+                        if (kk.elems != a.elems || vv.elems != a.elems || o.elems != a.elems || kk.dtype != a.dtype || vv.dtype != a.dtype) return 1;
+                        xs.kind = S_ATTENTION;
+                        xs.xp[1] = static_cast<int>(a.dims[a.rank - 2]); xs.xp[2] = static_cast<int>(a.dims[a.rank - 1]);
+                        xs.xp[3] = static_cast<int>(a.elems / (static_cast<size_t>(xs.xp[1]) * xs.xp[2]));     // batch * heads
+                    } else if (ext == EXT_CONV2D) {
+                        if (op.input_count < 2 || a.rank != 4 || V[xs.in1].rank != 4 || o.rank != 4) return -1;
+                        const Value& w = V[xs.in1];
+                        if (w.dims[3] != a.dims[3] || w.dtype != a.dtype) return 1;
+                        const int P = (static_cast<int>(a.dims[1]) - static_cast<int>(w.dims[1]) + 2 * xs.xp[0]) / xs.xp[2] + 1;
+                        const int Q = (static_cast<int>(a.dims[2]) - static_cast<int>(w.dims[2]) + 2 * xs.xp[1]) / xs.xp[3] + 1;
+                        if (o.dims[0] != a.dims[0] || o.dims[1] != P || o.dims[2] != Q || o.dims[3] != w.dims[0]) return -1;
+                        if (xs.in2 >= 0 && V[xs.in2].elems != static_cast<size_t>(w.dims[0])) return 1;
+                        xs.kind = S_CONV2D;
+                        xs.xp[5] = static_cast<int>(a.dims[0]); xs.xp[6] = static_cast<int>(a.dims[1]); xs.xp[7] = static_cast<int>(a.dims[2]);
+                        xs.xp[8] = static_cast<int>(a.dims[3]); xs.xp[9] = static_cast<int>(w.dims[0]); xs.xp[10] = static_cast<int>(w.dims[1]);
+                        xs.xp[11] = static_cast<int>(w.dims[2]);
+                    } else {   // EXT_FFN_FP8
+                        if (op.input_count < 5 || a.rank != 2 || a.dtype != PYC_DTYPE_BF16) return 1;
+                        const Value &w1 = V[xs.in1], &s1 = V[xs.in2], &w2 = V[xs.in3], &s2 = V[xs.in4];
+                        if (w1.rank != 2 || w2.rank != 2 || w1.dtype != PYC_DTYPE_I8 || w2.dtype != PYC_DTYPE_I8 || s1.dtype != PYC_DTYPE_F32 ||
+                            s2.dtype != PYC_DTYPE_F32 || w1.dims[0] != a.dims[1] || w2.dims[0] != w1.dims[1] || w2.dims[1] != a.dims[1] ||
+                            s1.elems != static_cast<size_t>(w1.dims[1]) || s2.elems != static_cast<size_t>(a.dims[1]) || o.elems != a.elems) return 1;
+                        xs.kind = S_FFN_FP8;
+                        xs.xp[0] = static_cast<int>(a.dims[0]); xs.xp[1] = static_cast<int>(a.dims[1]); xs.xp[2] = static_cast<int>(w1.dims[1]);
+                        Value ws; ws.kind = V_TEMP; ws.dtype = PYC_DTYPE_I8; ws.rank = 1;
+                        ws.bytes = pyc_b200_ffn_workspace_bytes(xs.xp[0], xs.xp[1], xs.xp[2]); ws.elems = ws.bytes; ws.dims[0] = static_cast<int64_t>(ws.bytes);
+                        xs.scratch = static_cast<int>(V.size());
+                        V.push_back(ws);                      // invalidates references into V: none is used below
+                    }
+                    S.push_back(xs);
+                    break;
+                }
                 if (a.elems % V[i].elems) return 1;
                 Step s; s.kind = S_REDUCE_SUM; s.in0 = op.input_ids[0]; s.rows = V[i].elems; s.cols = a.elems / V[i].elems; s.op_main = static_cast<int>(i);
                 s.out = static_cast<int>(i); V[i].kind = V_TEMP;
@@ -336,7 +427,8 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
     // has no live tenant; otherwise bump the peak).
     for (size_t si = 0; si < S.size(); ++si) {
         const Step& s = S[si];
-        const int ids[4] = {s.out, s.in0 >= 0 ? resolve(V, s.in0) : -1, s.in1 >= 0 ? resolve(V, s.in1) : -1, s.in2 >= 0 ? resolve(V, s.in2) : -1};
+        const int ids[7] = {s.out, s.in0 >= 0 ? resolve(V, s.in0) : -1, s.in1 >= 0 ? resolve(V, s.in1) : -1, s.in2 >= 0 ? resolve(V, s.in2) : -1,
+                            s.in3 >= 0 ? resolve(V, s.in3) : -1, s.in4 >= 0 ? resolve(V, s.in4) : -1, s.scratch};
         for (int id : ids) {
             if (id < 0 || V[id].kind != V_TEMP) continue;
             if (V[id].def_step < 0) V[id].def_step = static_cast<int>(si);
@@ -345,12 +437,12 @@ int build_plan(const pyc_ir_module* m, const pyc_tensor* inputs, size_t n_in, py
     }
     struct Req { int id; size_t bytes, off; int a, b; };
     std::vector<Req> reqs;
-    for (size_t i = 0; i < n; ++i) {
+    for (size_t i = 0; i < V.size(); ++i) {       // the IR ops' values, then the step-private workspaces
         Value& v = V[i];
         if (v.kind != V_TEMP) continue;
         if (v.def_step < 0) { v.def_step = 0; v.last_step = static_cast<int>(S.size()); }
         // Inputs whose upload is skipped (assume-static) must survive between runs: pin them for the whole plan.
-        if (m->ops[i].kind == PYC_IR_OP_INPUT && static_mask) { v.def_step = 0; v.last_step = static_cast<int>(S.size()); }
+        if (i < n && m->ops[i].kind == PYC_IR_OP_INPUT && static_mask) { v.def_step = 0; v.last_step = static_cast<int>(S.size()); }
         reqs.push_back({static_cast<int>(i), v.bytes, 0, v.def_step, v.last_step});
     }
     size_t peak = 0, total = 0;
@@ -531,6 +623,44 @@ int enqueue_plan(Plan& plan, DeviceContext* ctx, const pyc_tensor* inputs, pyc_t
                                      value_ptr(plan, ctx, inputs, outputs, s.out), s.rows, s.cols, 1e-5f, stream) != 0) return -1;
                 ++*kernels;
                 break;
+            case S_SOFTMAX:
+                if (launch_softmax(plan.values[s.out].dtype, value_ptr(plan, ctx, inputs, outputs, s.in0), value_ptr(plan, ctx, inputs, outputs, s.out),
+                                   s.rows, s.cols, stream) != 0) return -1;
+                s.symbol = std::string("b200_softmax_") + (plan.values[s.out].dtype == PYC_DTYPE_F32 ? "f32" : plan.values[s.out].dtype == PYC_DTYPE_BF16 ? "bf16" : "f16");
+                ++*kernels;
+                break;
+            case S_ATTENTION: {
+                const pyc_dtype dt = plan.values[s.out].dtype;
+                if (launch_attention(dt, s.xp[3], s.xp[1], s.xp[2], value_ptr(plan, ctx, inputs, outputs, s.in0), value_ptr(plan, ctx, inputs, outputs, s.in1),
+                                     value_ptr(plan, ctx, inputs, outputs, s.in2), value_ptr(plan, ctx, inputs, outputs, s.out),
+                                     1.0f / sqrtf(static_cast<float>(s.xp[2])), s.xp[0], stream, ctx->status_dev) != 0) return -1;
+                s.symbol = std::string("b200_attention_") + (dt == PYC_DTYPE_F32 ? "f32" : dt == PYC_DTYPE_BF16 ? "bf16" : "f16") + (s.xp[0] ? "_causal" : "");
+                ++*kernels;
+                break;
+            }
+            case S_CONV2D: {
+                const pyc_dtype dt = plan.values[s.out].dtype;
+                if (launch_conv2d(dt, s.xp[5], s.xp[6], s.xp[7], s.xp[8], s.xp[9], s.xp[10], s.xp[11], s.xp[0], s.xp[1], s.xp[2], s.xp[3],
+                                  value_ptr(plan, ctx, inputs, outputs, s.in0), value_ptr(plan, ctx, inputs, outputs, s.in1),
+                                  s.in2 >= 0 ? value_ptr(plan, ctx, inputs, outputs, s.in2) : nullptr, s.xp[4], value_ptr(plan, ctx, inputs, outputs, s.out),
+                                  stream, ctx->status_dev) != 0) return -1;
+                s.symbol = std::string("b200_conv2d_fprop_") + (dt == PYC_DTYPE_F32 ? "f32" : dt == PYC_DTYPE_BF16 ? "bf16" : "f16");
+                ++*kernels;
+                break;
+            }
+            case S_FFN_FP8: {
+                pyc_b200_ffn_args a;
+                memset(&a, 0, sizeof(a));
+                a.tokens = s.xp[0]; a.hidden = s.xp[1]; a.inner = s.xp[2];
+                a.x = value_ptr(plan, ctx, inputs, outputs, s.in0);
+                a.w1 = value_ptr(plan, ctx, inputs, outputs, s.in1); a.w1_scale = static_cast<const float*>(value_ptr(plan, ctx, inputs, outputs, s.in2));
+                a.w2 = value_ptr(plan, ctx, inputs, outputs, s.in3); a.w2_scale = static_cast<const float*>(value_ptr(plan, ctx, inputs, outputs, s.in4));
+                a.out = value_ptr(plan, ctx, inputs, outputs, s.out);
+                if (pyc_b200_ffn_block(&a, value_ptr(plan, ctx, inputs, outputs, s.scratch), plan.values[s.scratch].bytes, stream) != 0) return -1;
+                s.symbol = "b200_ffn_fp8_block";
+                *kernels += 4;
+                break;
+            }
             case S_REDUCE_SUM:
                 if (launch_reduce_sum(plan.values[s.out].dtype, value_ptr(plan, ctx, inputs, outputs, s.in0),
                                       value_ptr(plan, ctx, inputs, outputs, s.out), s.rows, s.cols, stream) != 0) return -1;
@@ -590,6 +720,7 @@ std::string describe_plan(const Plan& plan, const pyc_ir_module* m) {
             case S_BIAS_ACT: kernel = std::string("b200_bias_act_") + dtype_name(dt); break;
             case S_LAYERNORM: kernel = std::string("b200_layernorm_") + dtype_name(dt); break;
             case S_REDUCE_SUM: kernel = std::string("b200_reduce_sum_") + dtype_name(dt); break;
+            case S_SOFTMAX: case S_ATTENTION: case S_CONV2D: case S_FFN_FP8: kernel = s.symbol; break;
         }
         if (s.op_add >= 0) ops += " + " + op_ref(s.op_add);
         if (s.op_act >= 0) ops += " + " + op_ref(s.op_act);

@@ -64,7 +64,10 @@ __device__ __forceinline__ float act_fn(float v) {
 // Activation over a register vector; GELU takes the elements two at a time (packed fp32 pairs).
 template <int ACT, int VEC>
 __device__ __forceinline__ void act_vec(float (&v)[VEC]) {
-    if constexpr (ACT == PYC_B200_ACT_GELU && VEC % 2 == 0) {
+    if constexpr (ACT == PYC_B200_ACT_GELU && VEC == 8) {          // eight per 16 bytes: a 16-bit storage type
+#pragma unroll
+        for (int j = 0; j < VEC; j += 2) gelu_erf_x2_16bit(v[j], v[j + 1]);
+    } else if constexpr (ACT == PYC_B200_ACT_GELU && VEC % 2 == 0) {
 #pragma unroll
         for (int j = 0; j < VEC; j += 2) gelu_erf_x2(v[j], v[j + 1]);
     } else {
@@ -317,7 +320,8 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
                 for (int j = 0; j < VEC; ++j) mx = fmaxf(mx, f[j]);
             });
             mx = block_max<THREADS>(mx, scratch);
-            // exp(x - max) = 2^(x*log2e - max*log2e): one FMA + one MUFU op per element
+            // exp(x - max) = 2^(x*log2e - max*log2e): one FMA + one special-function op per element (arguments <= 0: the
+            // flush-to-zero form needs none of exp2f's range handling; 2 ulp)
             const float l2e = 1.4426950408889634f, mshift = -mx * l2e;
             float den = 0.0f;
             if constexpr (CACHED && VPT * VEC * (sizeof(T) == 4 ? 2 : 1) <= 32) {
@@ -329,7 +333,7 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
                         float f[VEC];
                         widen<T, VEC>(raw[i], f);
 #pragma unroll
-                        for (int j = 0; j < VEC; ++j) { e[i][j] = exp2f(fmaf(f[j], l2e, mshift)); den += e[i][j]; }
+                        for (int j = 0; j < VEC; ++j) { e[i][j] = ex2_approx(fmaf(f[j], l2e, mshift)); den += e[i][j]; }
                     }
                 }
                 const float inv = 1.0f / block_sum<THREADS>(den, scratch);
@@ -345,12 +349,12 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
             } else {
                 for_each([&](float (&f)[VEC], size_t) {
 #pragma unroll
-                    for (int j = 0; j < VEC; ++j) den += exp2f(fmaf(f[j], l2e, mshift));
+                    for (int j = 0; j < VEC; ++j) den += ex2_approx(fmaf(f[j], l2e, mshift));
                 });
                 const float inv = 1.0f / block_sum<THREADS>(den, scratch);
                 for_each([&](float (&f)[VEC], size_t vi) {
 #pragma unroll
-                    for (int j = 0; j < VEC; ++j) f[j] = exp2f(fmaf(f[j], l2e, mshift)) * inv;
+                    for (int j = 0; j < VEC; ++j) f[j] = ex2_approx(fmaf(f[j], l2e, mshift)) * inv;
                     store_vec<T, VEC>(orow + vi * VEC, f);
                 });
             }

@@ -102,7 +102,7 @@ __device__ __forceinline__ void fp8_epilogue_tile(const Fp8Epilogue& ep, uint32_
                 }
                 if (ep.act == PYC_B200_ACT_GELU) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) gelu_erf_x2(v[j], v[j + 1]);
+                    for (int j = 0; j < 32; j += 2) gelu_erf_x2_16bit(v[j], v[j + 1]);   // bf16 output
                 } else if (ep.act == PYC_B200_ACT_RELU) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);

@@ -244,7 +244,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 if (ep.act == PYC_B200_ACT_GELU) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) gelu_erf_x2(v[j], v[j + 1]);
+                    for (int j = 0; j < 32; j += 2) gelu_erf_x2_16bit(v[j], v[j + 1]);   // bf16 / f16 output
                 } else if (ep.act == PYC_B200_ACT_RELU) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);

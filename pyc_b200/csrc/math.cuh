@@ -73,6 +73,25 @@ __device__ __forceinline__ void gelu_erf_x2(float& v0, float& v1) {
     v1 = fmaf(-0.5f, fabsf(h1), fmaxf(v1, 0.0f));
 }
 
+// The same for results that are stored in a 16-bit type: a degree-4 exponent polynomial (three packed FMAs fewer per pair).
+// Fitted like the degree-7 one; absolute error of GELU 1.1e-6, relative error 1.1e-3 wherever |GELU| > 1e-3 -- under half a
+// bf16 step (2e-3) and about one f16 step (1e-3), so the stored value differs from the exact-erf result by at most one
+// rounding step of the 16-bit type.
+__device__ __forceinline__ void gelu_erf_x2_16bit(float& v0, float& v1) {
+    const float x0 = fminf(fabsf(v0) * 0.70710678118654752f, 4.2f), x1 = fminf(fabsf(v1) * 0.70710678118654752f, 4.2f);
+    const unsigned long long x = f32x2_pack(x0, x1);
+    unsigned long long q = f32x2_splat(-2.944164920e-03f);      // coefficients negated: the product below is -x * Q(x)
+    q = f32x2_fma(q, x, f32x2_splat(2.959006855e-02f));
+    q = f32x2_fma(q, x, f32x2_splat(-1.486656611e-01f));
+    q = f32x2_fma(q, x, f32x2_splat(-9.185093504e-01f));
+    q = f32x2_fma(q, x, f32x2_splat(-1.627889008e+00f));
+    float t0, t1;
+    f32x2_unpack(f32x2_mul(x, q), t0, t1);
+    const float h0 = v0 * ex2_approx(t0), h1 = v1 * ex2_approx(t1);   // v * erfc(x)
+    v0 = fmaf(-0.5f, fabsf(h0), fmaxf(v0, 0.0f));
+    v1 = fmaf(-0.5f, fabsf(h1), fmaxf(v1, 0.0f));
+}
+
 __device__ __forceinline__ float apply_activation(float v, int act) {
     if (act == 1 /* PYC_B200_ACT_RELU */) return v > 0.0f ? v : 0.0f;
     if (act == 2 /* PYC_B200_ACT_GELU */) return gelu_erf(v);

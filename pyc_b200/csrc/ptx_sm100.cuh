@@ -50,14 +50,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  `status` is a global int the host zeroes before launch; `where`
 // tags the call site.  About one second at B200 clocks before giving up; a
 // status already set by another thread ends the wait early.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int where) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int where, long long limit_cycles = 2000000000ll) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 0; it < (1u << 26); ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 255u) == 255u) {
             if (*reinterpret_cast<volatile int*>(status) != ST_OK) return false;
-            if (clock64() - t0 > 2000000000ll) break;
+            if (clock64() - t0 > limit_cycles) break;
         }
     }
     atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT | (where << 8));

@@ -26,6 +26,7 @@
 #include <vector>
 
 #include "internal.h"
+#include "ptx_sm100.cuh"
 #include "runtime.h"
 
 // PyC's kernel registry (src/compiler/runtime/kernel_registry.c) is looked up at run time in the process's global symbol
@@ -643,6 +644,19 @@ int autotune_db_load(const char* path) {
     return installed;
 }
 
+// ------------------------------------------------------- wait self-test ------
+// One CTA waits on an mbarrier that nobody arrives at, with a limit of `limit_cycles`: the wait gives up by itself,
+// records ST_WAIT_TIMEOUT with site 0x7f in the device status word and the kernel returns.  This is the path every
+// kernel's bounded waits take when a producer never shows up, exercised without making anything hang.
+__global__ void wait_selftest_kernel(int* status, long long limit_cycles) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        fence_barrier_init();
+        mbar_wait(smem_u32(&bar), 0, status, 0x7f, limit_cycles);
+    }
+}
+
 // ------------------------------------------------------------- autotune ------
 // Operands for timing: values ~ N(0, 0.02^2) (sum of four uniforms, counter-based hash of the element index), so that the
 // tensor cores toggle as they do on real activations/weights.  All-zero operands draw less power and clock higher on a
@@ -814,6 +828,15 @@ int pyc_b200_autotune_gemm(pyc_dtype dtype, int M, int N, int K, int iters, char
 }
 
 int pyc_b200_autotune_db_load(const char* path) { return autotune_db_load(path); }
+
+int pyc_b200_selftest_wait_timeout(int limit_us, void* stream) {
+    DeviceContext* c = current_context();
+    if (!c) return -1;
+    if (limit_us < 1 || limit_us > 1000000) { set_error("wait self-test: limit must be 1 .. 1000000 us"); return -1; }
+    wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(c->status_dev, static_cast<long long>(limit_us) * 2000);   // ~2 GHz
+    B200_CUDA_OK(cudaGetLastError());
+    return 0;
+}
 
 int pyc_b200_get_runtime_info(pyc_b200_runtime_info* out) {
     if (!out) return -1;

@@ -141,7 +141,30 @@ class FfnBlock:
                              self.comm.vtable if self.comm else None, self.comm.handle if self.comm else None, self.world, self.rank, stream=s)
         return self.out
 
+    def capture(self, x_dev):
+        """Record one run() on `x_dev` (its address is baked in) as a CUDA graph -- the four kernels, the collective or the
+        peer exchange with its barriers -- and return a callable that replays it on torch's current stream and returns the
+        output tensor.  Removes the launch gaps between the block's kernels (~25 us of a 0.9 ms block on one GPU, more of
+        the shorter per-rank blocks).  Every rank must capture and replay in step, as with any collective."""
+        torch = self.torch
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):                       # first-use set-up (kernel attributes, NCCL channels) outside the capture
+                self.run(x_dev, stream=side.cuda_stream)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            out = self.run(x_dev, stream=torch.cuda.current_stream().cuda_stream)
+        self._graph, self._graph_x = graph, x_dev    # keep both alive
+
+        def replay():
+            graph.replay()
+            return out
+        return replay
+
     def close(self):
+        self._graph = None
         if self.peer is not None:
             self.peer.close(); self.peer = None
         if self._own_comm and self.comm is not None:

@@ -63,6 +63,14 @@ class ModuleBuilder:
         s = self._shape(a)
         return self._add(abi.OP_REDUCE_SUM, name or f"rsum_{self.module.op_count}", self._dtype(a), s[:-1] or [1], (a,))
 
+    def extended(self, name, dtype, shape, inputs):
+        """An op PyC's IR has no kind for, carried by a REDUCE_SUM op whose name starts with "b200." and whose declared
+        shape is its output shape (the backend's name-keyed side table): b200.softmax, b200.attention[.causal],
+        b200.conv2d.p<ph>x<pw>.s<sh>x<sw>[.relu], b200.ffn_fp8."""
+        if not name.startswith("b200."):
+            raise ValueError("extended op names start with 'b200.'")
+        return self._add(abi.OP_REDUCE_SUM, name, dtype, shape, tuple(inputs))
+
     def output(self, a, name=None):
         return self._add(abi.OP_OUTPUT, name or f"out_{self.module.op_count}", self._dtype(a), self._shape(a), (a,))
 

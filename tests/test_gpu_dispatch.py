@@ -222,3 +222,29 @@ def test_pinned_host_tensors_take_the_pipelined_path_and_match(backend, oracle_l
     for key in (("pipelined", 0), ("pipelined_stream", 0)):
         piped = workloads.bf16_bits_to_f32(results[key].view(np.uint16))
         assert np.abs(piped - serial).max() <= 2e-2 * np.abs(serial).max()
+
+
+def test_a_wait_that_runs_out_is_reported_not_hung(backend):
+    """A kernel's bounded wait on a barrier nobody arrives at gives up by itself (about 50 us here), the kernel returns, and the
+    host sees where: the status word carries (site << 8) | 1.  A dispatch that finds the word set reports
+    b200_kernel_wait_timeout as an ERROR (never a CPU fallback), clears it, and the next dispatch is fine again."""
+    import torch
+    torch.cuda.synchronize()
+    assert backend.device_status() == 0
+    backend.selftest_wait_timeout(50)
+    torch.cuda.synchronize()
+    assert backend.device_status() == (0x7f << 8) | 1
+    assert backend.device_status() == 0                      # read-and-clear
+    lhs = np.array([[1, -2], [3, 4]], np.float32); rhs = np.array([[2, 1], [-1, 3]], np.float32); bias = np.array([0.5, -1.5], np.float32)
+    mod = ir.matmul_bias_act(abi.DTYPE_F32, 2, 2, 2, bias="row", act="relu")
+    out = np.zeros((2, 2), np.float32)
+    arrays = [lhs, rhs, bias]
+    _host_tensors = lambda arrs: [_host(a, 1) for a in arrs]
+    backend.selftest_wait_timeout(50)
+    torch.cuda.synchronize()
+    st, trace = backend.dispatch(mod, _host_tensors(arrays), _host_tensors([out]), require_gpu=False)
+    assert st == abi.DISPATCH_ERROR and trace.fallback_to_cpu == 0
+    assert trace.reason.decode() == "b200_kernel_wait_timeout:0x7f01"
+    st, trace = backend.dispatch(mod, _host_tensors(arrays), _host_tensors([out]))
+    assert st == abi.DISPATCH_OK
+    np.testing.assert_allclose(out.reshape(-1), [4.5, 0.0, 2.5, 13.5], atol=1e-5)

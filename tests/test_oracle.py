@@ -149,3 +149,23 @@ def test_module_walk_rejects_what_pyc_rejects(oracle_lib):
         oracle_lib.run_module(b.module, [], [((4,), abi.DTYPE_F32)])
     with pytest.raises(ValueError):  # ir.c:80-89: inputs must reference earlier ops
         ir.ModuleBuilder()._add(abi.OP_RELU, "r", abi.DTYPE_F32, [4], (0,))
+
+
+def test_gelu_and_layernorm_definitions_agree_with_torch_fp64(oracle_lib):
+    """The reference has no executor for GELU / LAYERNORM; its only semantic hint is torch.nn.GELU() / nn.LayerNorm(hidden) in its
+    benchmark workloads (benchmark/benchmarks/gpu/workloads/standard_workload.py:58-62).  The oracle's definitions (exact-erf
+    GELU; last axis, biased variance, eps 1e-5 inside the root, optional affine) are held to torch's fp64 results of those two
+    modules.  This is the most the reference allows: conv2d, attention and fp8 stay unpinned."""
+    import torch
+    from pyc_b200 import workloads
+    x = workloads.normal((37, 300), 4242, 3.0)
+    g = torch.nn.functional.gelu(torch.from_numpy(x).double()).numpy()
+    np.testing.assert_allclose(oracle_lib.gelu(x), g, rtol=2e-6, atol=2e-7)
+    gamma, beta = workloads.normal((300,), 4243), workloads.normal((300,), 4244)
+    ln = torch.nn.LayerNorm(300, eps=1e-5).double()
+    with torch.no_grad():
+        ln.weight.copy_(torch.from_numpy(gamma).double()); ln.bias.copy_(torch.from_numpy(beta).double())
+        want_affine = ln(torch.from_numpy(x).double()).numpy()
+        want_plain = torch.nn.functional.layer_norm(torch.from_numpy(x).double(), (300,), eps=1e-5).numpy()
+    np.testing.assert_allclose(oracle_lib.layernorm(x, gamma, beta), want_affine, rtol=1e-5, atol=2e-6)
+    np.testing.assert_allclose(oracle_lib.layernorm(x), want_plain, rtol=1e-5, atol=2e-6)
