@@ -549,8 +549,75 @@ def vtable_all_reduce(comm):
     return call
 
 
+def run_only(args):
+    """--only <kernel>: a few launches of ONE kernel through the C-ABI on seeded device inputs, for profilers (small cases
+    that keep a capture short) and quick timing.  Prints one JSON line; not the benchmark."""
+    import torch
+    from pyc_b200 import abi, backend
+    torch.cuda.set_device(0)
+    backend.load()
+    dims = [int(v) for v in args.shape.split(",")] if args.shape else []
+    g = torch.Generator(device="cuda"); g.manual_seed(0x5EED0070)
+    dt = {"bf16": (abi.DTYPE_BF16, torch.bfloat16), "f16": (abi.DTYPE_F16, torch.float16), "f32": (abi.DTYPE_F32, torch.float32)}[args.dtype]
+    rnd = lambda shape, std=1.0: (torch.randn(shape, generator=g, device="cuda") * std).to(dt[1])
+    if args.only == "gemm":
+        m, n, k = dims or [8192, 8192, 2048]
+        a, b, bias, d = rnd((m, k), 0.02), rnd((k, n), 0.02), rnd((n,), 0.02), torch.zeros((m, n), dtype=dt[1], device="cuda")
+        mode, act = {"none": (abi.ADD_NONE, abi.ACT_NONE), "bias_relu": (abi.ADD_ROW_BIAS, abi.ACT_RELU), "bias_gelu": (abi.ADD_ROW_BIAS, abi.ACT_GELU)}[args.epilogue]
+        run = lambda: backend.gemm(dt[0], m, n, k, a.data_ptr(), b.data_ptr(), d.data_ptr(), add=bias.data_ptr(), add_mode=mode, act=act, symbol=args.symbol)
+        work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+    elif args.only == "attention":
+        bh, seq, d_ = dims or [64, 2048, 128]
+        q, k_, v, o = rnd((bh, seq, d_)), rnd((bh, seq, d_)), rnd((bh, seq, d_)), torch.zeros((bh, seq, d_), dtype=dt[1], device="cuda")
+        run = lambda: backend.attention(dt[0], bh, seq, d_, q.data_ptr(), k_.data_ptr(), v.data_ptr(), o.data_ptr(), d_ ** -0.5, args.causal)
+        work, unit = 4.0 * bh * d_ * (seq * (seq + 1) / 2 if args.causal else seq * seq) / 1e12, "TFLOP/s"
+    elif args.only == "conv2d":
+        n, h, c, kf = dims or [64, 56, 64, 64]
+        x, w, b, o = rnd((n, h, h, c)), rnd((kf, 3, 3, c), (2.0 / (9 * c)) ** 0.5), rnd((kf,), 0.1), torch.zeros((n, h, h, kf), dtype=dt[1], device="cuda")
+        run = lambda: backend.conv2d(dt[0], n, h, h, c, kf, 3, 3, (1, 1), (1, 1), x.data_ptr(), w.data_ptr(), b.data_ptr(), True, o.data_ptr())
+        work, unit = 2.0 * n * h * h * c * kf * 9 / 1e12, "TFLOP/s"
+    elif args.only in ("add", "bias_gelu", "layernorm", "softmax"):
+        rows, cols = dims or [16384, 8192]
+        x, y, bias, o = rnd((rows, cols)), rnd((rows, cols)), rnd((cols,)), torch.zeros((rows, cols), dtype=dt[1], device="cuda")
+        run = {"add": lambda: backend.add(dt[0], x.data_ptr(), y.data_ptr(), o.data_ptr(), rows * cols),
+               "bias_gelu": lambda: backend.bias_act(dt[0], x.data_ptr(), bias.data_ptr(), abi.ADD_ROW_BIAS, abi.ACT_GELU, o.data_ptr(), rows, cols),
+               "layernorm": lambda: backend.layernorm(dt[0], x.data_ptr(), None, None, o.data_ptr(), rows, cols),
+               "softmax": lambda: backend.softmax(dt[0], x.data_ptr(), o.data_ptr(), rows, cols)}[args.only]
+        work, unit = (3 if args.only == "add" else 2) * rows * cols * x.element_size() / 1e9, "GB/s"
+    elif args.only == "gemm_fp8":
+        m, n, k = dims or [8192, 8192, 2048]
+        a = torch.randint(0, 120, (m, k), dtype=torch.uint8, device="cuda", generator=g); b = torch.randint(0, 120, (k, n), dtype=torch.uint8, device="cuda", generator=g)
+        rs, cs, d = torch.ones(m, device="cuda"), torch.ones(n, device="cuda"), torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        run = lambda: backend.gemm_fp8(m, n, k, a.data_ptr(), b.data_ptr(), d.data_ptr(), rs.data_ptr(), cs.data_ptr(), None, abi.ACT_GELU)
+        work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+    else:
+        raise SystemExit(f"--only {args.only}: unknown kernel")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(args.warmup):
+        run()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for e0, e1 in ev:
+        if not args.warm:
+            flush.zero_()
+        e0.record(); run(); e1.record()
+    torch.cuda.synchronize()
+    assert backend.device_status() == 0
+    ts = sorted(a_.elapsed_time(b_) for a_, b_ in ev)
+    ms = ts[len(ts) // 2]
+    print(json.dumps({"only": args.only, "shape": args.shape, "dtype": args.dtype, "ms_median": ms, "rate": work / (ms * 1e-3), "unit": unit,
+                      "launches": args.steps + args.warmup, "l2": "warm" if args.warm else "flushed before every launch"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None, help="gemm | attention | conv2d | add | bias_gelu | layernorm | softmax | gemm_fp8: one kernel, for profilers")
+    ap.add_argument("--shape", default=None, help="--only: comma-separated sizes (gemm M,N,K; attention heads,seq,d; conv2d N,H,C,K; rows,cols)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16", "f32"])
+    ap.add_argument("--epilogue", default="bias_gelu", choices=["none", "bias_relu", "bias_gelu"])
+    ap.add_argument("--symbol", default=None)
+    ap.add_argument("--causal", type=int, default=1)
+    ap.add_argument("--warm", type=int, default=0, help="--only: 1 = do not flush L2 between launches")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
@@ -561,6 +628,9 @@ def main():
     rank = int(os.environ.get("RANK", "0")); local = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         reference_arm(args, rank, world)
+        return
+    if args.only:
+        run_only(args)
         return
     args.warmup = max(args.warmup, 3)
 

@@ -758,45 +758,47 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
     const bool replay_enabled = env_default_true("PYC_CUDA_ENABLE_GRAPH_REPLAY");
 
     // Key: module content + tensor descriptors + switches.
-    uint64_t base = 1469598103934665603ull;
-    base = fnv1a(base, &module->op_count, sizeof(module->op_count));
+    // Two independent 64-bit hashes of the same key material: `base` indexes the cache, `check` is stored with the entry and
+    // compared on a hit, so a collision of the index cannot replay another call's graph.
+    uint64_t base = 1469598103934665603ull, check = 0x84222325cbf29ce4ull;
+    { base = fnv1a(base, &module->op_count, sizeof(module->op_count)); check = fnv1a(check * 31 + 7, &module->op_count, sizeof(module->op_count)); }
     for (size_t i = 0; i < module->op_count; ++i) {
         const pyc_ir_op& op = module->ops[i];
-        base = fnv1a(base, &op.kind, sizeof(op.kind));
-        base = fnv1a(base, &op.dtype, sizeof(op.dtype));
-        base = fnv1a(base, &op.shape.rank, sizeof(op.shape.rank));
-        base = fnv1a(base, op.shape.dims, sizeof(int64_t) * op.shape.rank);
-        base = fnv1a(base, &op.input_count, sizeof(op.input_count));
-        base = fnv1a(base, op.input_ids, sizeof(int) * op.input_count);
+        { base = fnv1a(base, &op.kind, sizeof(op.kind)); check = fnv1a(check * 31 + 7, &op.kind, sizeof(op.kind)); }
+        { base = fnv1a(base, &op.dtype, sizeof(op.dtype)); check = fnv1a(check * 31 + 7, &op.dtype, sizeof(op.dtype)); }
+        { base = fnv1a(base, &op.shape.rank, sizeof(op.shape.rank)); check = fnv1a(check * 31 + 7, &op.shape.rank, sizeof(op.shape.rank)); }
+        { base = fnv1a(base, op.shape.dims, sizeof(int64_t) * op.shape.rank); check = fnv1a(check * 31 + 7, op.shape.dims, sizeof(int64_t) * op.shape.rank); }
+        { base = fnv1a(base, &op.input_count, sizeof(op.input_count)); check = fnv1a(check * 31 + 7, &op.input_count, sizeof(op.input_count)); }
+        { base = fnv1a(base, op.input_ids, sizeof(int) * op.input_count); check = fnv1a(check * 31 + 7, op.input_ids, sizeof(int) * op.input_count); }
     }
     // Tensor descriptors: address, size, where the memory lives, and the dtype/shape the planner reads when the INPUT op
     // itself carries none (two calls that differ only there must not share a plan).
     auto hash_tensor = [&](const pyc_tensor& t, MemKind mk) {
-        base = fnv1a(base, &t.data, sizeof(void*)); base = fnv1a(base, &t.size_bytes, sizeof(size_t)); base = fnv1a(base, &mk, sizeof(MemKind));
-        base = fnv1a(base, &t.dtype, sizeof(t.dtype)); base = fnv1a(base, &t.shape.rank, sizeof(t.shape.rank));
-        base = fnv1a(base, t.shape.dims, sizeof(int64_t) * (t.shape.rank <= PYC_IR_MAX_DIMS ? t.shape.rank : PYC_IR_MAX_DIMS));
+        { base = fnv1a(base, &t.data, sizeof(void*)); check = fnv1a(check * 31 + 7, &t.data, sizeof(void*)); } { base = fnv1a(base, &t.size_bytes, sizeof(size_t)); check = fnv1a(check * 31 + 7, &t.size_bytes, sizeof(size_t)); } { base = fnv1a(base, &mk, sizeof(MemKind)); check = fnv1a(check * 31 + 7, &mk, sizeof(MemKind)); }
+        { base = fnv1a(base, &t.dtype, sizeof(t.dtype)); check = fnv1a(check * 31 + 7, &t.dtype, sizeof(t.dtype)); } { base = fnv1a(base, &t.shape.rank, sizeof(t.shape.rank)); check = fnv1a(check * 31 + 7, &t.shape.rank, sizeof(t.shape.rank)); }
+        { base = fnv1a(base, t.shape.dims, sizeof(int64_t) * (t.shape.rank <= PYC_IR_MAX_DIMS ? t.shape.rank : PYC_IR_MAX_DIMS)); check = fnv1a(check * 31 + 7, t.shape.dims, sizeof(int64_t) * (t.shape.rank <= PYC_IR_MAX_DIMS ? t.shape.rank : PYC_IR_MAX_DIMS)); }
     };
     for (size_t i = 0; i < n_in; ++i) hash_tensor(inputs[i], in_mem[i]);
     for (size_t i = 0; i < n_out; ++i) hash_tensor(outputs[i], out_mem[i]);
-    base = fnv1a(base, &skip_out, sizeof(skip_out));
+    { base = fnv1a(base, &skip_out, sizeof(skip_out)); check = fnv1a(check * 31 + 7, &skip_out, sizeof(skip_out)); }
     // Switches that change which kernel a captured graph holds.
     for (const char* name : {"PYC_B200_AUTOTUNE", "PYC_B200_GEMM_L2_HINTS", "PYC_B200_GEMM_GROUP_M", "PYC_CUDA_BF16_GEMM_SYMBOL",
                              "PYC_CUDA_ENABLE_PROMOTED_GEMM", "PYC_B200_REGISTRY_SELECT", "PYC_B200_PIPELINE_CHUNKS"}) {
         const char* v = getenv(name);
-        base = fnv1a(base, name, strlen(name));
-        if (v) base = fnv1a(base, v, strlen(v) + 1);
+        { base = fnv1a(base, name, strlen(name)); check = fnv1a(check * 31 + 7, name, strlen(name)); }
+        if (v) { base = fnv1a(base, v, strlen(v) + 1); check = fnv1a(check * 31 + 7, v, strlen(v) + 1); }
     }
     {
         const uint64_t epoch = selection_epoch();   // a new autotune winner invalidates graphs captured with the old choice
-        base = fnv1a(base, &epoch, sizeof(epoch));
+        { base = fnv1a(base, &epoch, sizeof(epoch)); check = fnv1a(check * 31 + 7, &epoch, sizeof(epoch)); }
         if (!env_is_false_value("PYC_CUDA_ENABLE_PROMOTED_GEMM")) {
             std::string promoted;                   // so does a promotion made through PyC's registry since the capture
-            if (registry_promoted_symbol("matmul", &promoted)) base = fnv1a(base, promoted.data(), promoted.size());
+            if (registry_promoted_symbol("matmul", &promoted)) { base = fnv1a(base, promoted.data(), promoted.size()); check = fnv1a(check * 31 + 7, promoted.data(), promoted.size()); }
         }
     }
     // PYC_B200_PIPELINE_HOST_COPIES=0 keeps uploads, kernel and downloads strictly one after another.
     const bool pipeline_enabled = env_default_true("PYC_B200_PIPELINE_HOST_COPIES");
-    base = fnv1a(base, &pipeline_enabled, sizeof(pipeline_enabled));
+    { base = fnv1a(base, &pipeline_enabled, sizeof(pipeline_enabled)); check = fnv1a(check * 31 + 7, &pipeline_enabled, sizeof(pipeline_enabled)); }
 
     // PYC_CUDA_ASSUME_STATIC_LHS/RHS (cuda_backend.c:2521-2522, 2625-2636): once a host operand has
     // been uploaded for this module and nothing else used the arena since, do not upload it again.
@@ -813,6 +815,7 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
     std::shared_ptr<Plan> plan_holder;
     if (replay_enabled) {
         auto hit = ctx->graphs.find(key);
+        if (hit != ctx->graphs.end() && hit->second.check != check) { cudaGraphExecDestroy(hit->second.exec); ctx->graphs.erase(hit); hit = ctx->graphs.end(); }
         if (hit != ctx->graphs.end() && hit->second.plan) plan_holder = std::static_pointer_cast<Plan>(hit->second.plan);
     }
     if (!plan_holder) {
@@ -872,6 +875,7 @@ int run_on_gpu(const pyc_ir_module* module, const pyc_tensor* inputs, size_t n_i
             if (ie != cudaSuccess) { snprintf(reason, reason_size, "b200_graph_instantiate_failed:%s", cudaGetErrorString(ie)); cudaGetLastError(); return -1; }
             cg.kernels = kernels;
             cg.plan = plan_holder;
+            cg.check = check;
             it = ctx->graphs.emplace(key, cg).first;
         } else {
             replayed = true;

@@ -136,12 +136,18 @@ gemm_simt_kernel(SimtParams p) {
     }
 }
 
-// Latency variant for small fp32 problems (the 512^3 graph): 32 x 64 tile, 128 threads, 4 x 4 outputs per thread,
-// operands brought in with 16-byte cp.async into a 3-stage ring of 32-deep k-slices, 16-byte shared-memory reads
-// (8 loads per 64 FMAs).  One wave of small CTAs covers most of the SMs; the ring hides the L2 latency that the
-// register-prefetch kernel above exposes when only one CTA sits on an SM.  Needs K % 4 == 0, N % 4 == 0, 16-byte
-// aligned A and B, row-major B.
-constexpr int LBM = 32, LBN = 64, LBK = 32, LSTAGES = 3, LPAD = 4;
+// Latency variant for small fp32 problems (the 512^3 graph): 32 x 64 tile, 4 x 4 outputs per thread, operands brought
+// in with 16-byte cp.async into a 3-stage ring of 32-deep k-slices, 16-byte shared-memory reads (8 loads per 64 FMAs).
+// One wave of small CTAs covers most of the SMs, which leaves one CTA per SM: with 128 threads that is ONE warp per
+// scheduler, and a lone warp issues its dependent FMA chain at well under half rate.  So the CTA has 512 threads:
+// four groups of 128 each take a quarter of every k-slice (two of its eight 4-deep steps) into their own accumulators,
+// and the four partial tiles are summed through shared memory once, after the last slice.  Within a group k ascends;
+// the four partial sums are added in group order.  Needs K % 4 == 0, N % 4 == 0, 16-byte aligned A, B and D,
+// row-major B.
+constexpr int LBM = 32, LBN = 64, LBK = 32, LSTAGES = 3, LPAD = 4, LGROUPS = 4, LTHREADS = 128 * LGROUPS;
+constexpr int L_A_FLOATS = LBM * (LBK + LPAD), L_B_FLOATS = LBK * LBN;
+static_assert(LSTAGES * (L_A_FLOATS + L_B_FLOATS) >= LGROUPS * LBM * LBN, "the partial tiles reuse the operand ring");
+static_assert((LBK / 4) % LGROUPS == 0, "every group takes the same number of 4-deep steps of a slice");
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -151,30 +157,29 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool va
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(LTHREADS)
 gemm_simt_latency_kernel(SimtParams p) {
-    __shared__ __align__(16) float As[LSTAGES][LBM][LBK + LPAD];
-    __shared__ __align__(16) float Bs[LSTAGES][LBK][LBN];
+    __shared__ __align__(16) float ring[LSTAGES * (L_A_FLOATS + L_B_FLOATS)];
+    auto As = [&](int buf, int r, int k) -> float* { return ring + buf * L_A_FLOATS + r * (LBK + LPAD) + k; };
+    auto Bs = [&](int buf, int k, int c) -> float* { return ring + LSTAGES * L_A_FLOATS + buf * L_B_FLOATS + k * LBN + c; };
     const float* A = reinterpret_cast<const float*>(p.A);
     const float* B = reinterpret_cast<const float*>(p.B);
-    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int tid = threadIdx.x, group = tid >> 7, lt = tid & 127, tx = lt & 15, ty = lt >> 4;
     const int m0 = blockIdx.y * LBM, n0 = blockIdx.x * LBN;
     const int M = p.M, N = p.N, K = p.K;
     const int steps = (K + LBK - 1) / LBK;
 
     auto issue = [&](int step, int buf) {
         const int k0 = step * LBK;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {   // A: 32 rows x 8 chunks of 4 floats
-            const int c = tid + i * 128, r = c >> 3, kc = (c & 7) * 4;
+        if (tid < 256) {                // A: 32 rows x 8 chunks of 4 floats
+            const int r = tid >> 3, kc = (tid & 7) * 4;
             const bool ok = (m0 + r) < M && (k0 + kc) < K;
-            cp_async16(&As[buf][r][kc], ok ? A + static_cast<size_t>(m0 + r) * K + k0 + kc : A, ok);
+            cp_async16(As(buf, r, kc), ok ? A + static_cast<size_t>(m0 + r) * K + k0 + kc : A, ok);
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {   // B: 32 k-rows x 16 chunks of 4 floats
-            const int c = tid + i * 128, r = c >> 4, nc = (c & 15) * 4;
+        {                               // B: 32 k-rows x 16 chunks of 4 floats
+            const int r = tid >> 4, nc = (tid & 15) * 4;
             const bool ok = (k0 + r) < K && (n0 + nc) < N;
-            cp_async16(&Bs[buf][r][nc], ok ? B + static_cast<size_t>(k0 + r) * N + n0 + nc : B, ok);
+            cp_async16(Bs(buf, r, nc), ok ? B + static_cast<size_t>(k0 + r) * N + n0 + nc : B, ok);
         }
     };
 
@@ -194,14 +199,15 @@ gemm_simt_latency_kernel(SimtParams p) {
         cp_async_commit();
         const int buf = step % LSTAGES;
 #pragma unroll
-        for (int k4 = 0; k4 < LBK / 4; ++k4) {
+        for (int q = 0; q < LBK / 4 / LGROUPS; ++q) {
+            const int k4 = group * (LBK / 4 / LGROUPS) + q;
             float4 a[4], b[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(&As[buf][ty * 4 + i][k4 * 4]);
+            for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(As(buf, ty * 4 + i, k4 * 4));
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) b[kk] = *reinterpret_cast<const float4*>(&Bs[buf][k4 * 4 + kk][tx * 4]);
+            for (int kk = 0; kk < 4; ++kk) b[kk] = *reinterpret_cast<const float4*>(Bs(buf, k4 * 4 + kk, tx * 4));
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {   // ascending k inside the slice, as everywhere else
+            for (int i = 0; i < 4; ++i) {   // ascending k inside the group's share of the slice
                 const float av[4] = {a[i].x, a[i].y, a[i].z, a[i].w};
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
@@ -212,24 +218,37 @@ gemm_simt_latency_kernel(SimtParams p) {
         }
     }
 
+    // Partial tiles through the (now idle) ring, then every thread finishes one float4 of the 32 x 64 tile.
+    cp_async_wait<0>();
+    __syncthreads();
+    float* part = ring;                        // [group][LBM][LBN]
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<float4*>(part + (group * LBM + ty * 4 + i) * LBN + tx * 4) =
+            make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    __syncthreads();
+    const int orow = tid >> 4, ocol = (tid & 15) * 4;
+    float4 s = *reinterpret_cast<const float4*>(part + orow * LBN + ocol);
+#pragma unroll
+    for (int g = 1; g < LGROUPS; ++g) {
+        const float4 t = *reinterpret_cast<const float4*>(part + (g * LBM + orow) * LBN + ocol);
+        s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+
     float* D = reinterpret_cast<float*>(p.D);
     const float* add = reinterpret_cast<const float*>(p.add);
     const float sadd = p.add_mode == PYC_B200_ADD_SCALAR ? p.add_scale * __ldg(add) : 0.0f;
-    const int c0 = n0 + tx * 4;
+    const int r = m0 + orow, c0 = n0 + ocol;
+    if (r >= M || c0 >= N) return;             // N % 4 == 0: a thread's four columns are in or out together
+    float v[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = m0 + ty * 4 + i;
-        if (r >= M || c0 >= N) continue;   // N % 4 == 0: a thread's four columns are in or out together
-        float v[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            v[j] = p.alpha * acc[i][j] + sadd;
-            if (p.add_mode == PYC_B200_ADD_ROW_BIAS) v[j] += p.add_scale * __ldg(add + c0 + j);
-            else if (p.add_mode == PYC_B200_ADD_MATRIX) v[j] += p.add_scale * __ldg(add + static_cast<size_t>(r) * N + c0 + j);
-            v[j] = act_fn(v[j], p.act);
-        }
-        *reinterpret_cast<float4*>(D + static_cast<size_t>(r) * N + c0) = make_float4(v[0], v[1], v[2], v[3]);
+    for (int j = 0; j < 4; ++j) {
+        v[j] = p.alpha * v[j] + sadd;
+        if (p.add_mode == PYC_B200_ADD_ROW_BIAS) v[j] += p.add_scale * __ldg(add + c0 + j);
+        else if (p.add_mode == PYC_B200_ADD_MATRIX) v[j] += p.add_scale * __ldg(add + static_cast<size_t>(r) * N + c0 + j);
+        v[j] = act_fn(v[j], p.act);
     }
+    *reinterpret_cast<float4*>(D + static_cast<size_t>(r) * N + c0) = make_float4(v[0], v[1], v[2], v[3]);
 }
 
 template <typename T, int BM, int BN, int TM, int TN>
@@ -252,7 +271,7 @@ int launch_typed(const GemmConfig& cfg, const SimtParams& sp, cudaStream_t strea
         if (cfg.bm == 32 && cfg.bn == 64 && cfg.bk == 32) {
             if (!latency_kernel_ok(sp)) { set_error("simt_async_32x64x32 needs row-major B, K %% 4 == 0, N %% 4 == 0 and 16-byte aligned pointers"); return -1; }
             dim3 grid((sp.N + LBN - 1) / LBN, (sp.M + LBM - 1) / LBM);
-            gemm_simt_latency_kernel<<<grid, 128, 0, stream>>>(sp);
+            gemm_simt_latency_kernel<<<grid, LTHREADS, 0, stream>>>(sp);
             B200_CUDA_OK(cudaGetLastError());
             count_launch();
             return 0;

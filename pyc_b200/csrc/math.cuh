@@ -78,8 +78,11 @@ __device__ __forceinline__ void gelu_erf_x2(float& v0, float& v1) {
 // bf16 step (2e-3) and about one f16 step (1e-3), so the stored value differs from the exact-erf result by at most one
 // rounding step of the 16-bit type.
 __device__ __forceinline__ void gelu_erf_x2_16bit(float& v0, float& v1) {
-    const float x0 = fminf(fabsf(v0) * 0.70710678118654752f, 4.2f), x1 = fminf(fabsf(v1) * 0.70710678118654752f, 4.2f);
-    const unsigned long long x = f32x2_pack(x0, x1);
+    // No clamp of x here: beyond the fitted range the polynomial keeps growing (Q(5) = 8.1, Q(6) = 9.9, ...), so 2^(-x Q)
+    // underflows to zero as erfc does (absolute error < 1e-12 * |v|), and for huge |v| the chain saturates to -inf -> 0.
+    const float a0 = fabsf(v0), a1 = fabsf(v1);
+    const unsigned long long av = f32x2_pack(a0, a1);
+    const unsigned long long x = f32x2_mul(av, f32x2_splat(0.70710678118654752f));
     unsigned long long q = f32x2_splat(-2.944164920e-03f);      // coefficients negated: the product below is -x * Q(x)
     q = f32x2_fma(q, x, f32x2_splat(2.959006855e-02f));
     q = f32x2_fma(q, x, f32x2_splat(-1.486656611e-01f));
@@ -87,9 +90,9 @@ __device__ __forceinline__ void gelu_erf_x2_16bit(float& v0, float& v1) {
     q = f32x2_fma(q, x, f32x2_splat(-1.627889008e+00f));
     float t0, t1;
     f32x2_unpack(f32x2_mul(x, q), t0, t1);
-    const float h0 = v0 * ex2_approx(t0), h1 = v1 * ex2_approx(t1);   // v * erfc(x)
-    v0 = fmaf(-0.5f, fabsf(h0), fmaxf(v0, 0.0f));
-    v1 = fmaf(-0.5f, fabsf(h1), fmaxf(v1, 0.0f));
+    const unsigned long long e = f32x2_pack(ex2_approx(t0), ex2_approx(t1));          // erfc(x)
+    const unsigned long long pos = f32x2_pack(fmaxf(v0, 0.0f), fmaxf(v1, 0.0f));
+    f32x2_unpack(f32x2_fma(f32x2_mul(av, e), f32x2_splat(-0.5f), pos), v0, v1);       // max(v, 0) - 0.5 |v| erfc(x)
 }
 
 __device__ __forceinline__ float apply_activation(float v, int act) {

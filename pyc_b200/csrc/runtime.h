@@ -20,6 +20,7 @@ struct CachedGraph {
     cudaGraphExec_t exec = nullptr;
     size_t kernels = 0;
     size_t replays = 0;
+    uint64_t check = 0;           // second hash of the key material, compared on every hit
     std::shared_ptr<void> plan;   // the dispatch layer's step list for this key (opaque here)
 };
 
