@@ -27,7 +27,7 @@ M = N = K = 8192
 FLOP_PER_STEP = 2.0 * M * N * K
 ALGO_BYTES = 3 * M * N * 2 + N * 2          # A, B, D bf16 + bias
 # dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of the default kernel (b200_gemm_bf16_tc2_256x256x64_s6)
-NCU_TRAFFIC_BYTES = 1104316160 + 126199296
+NCU_TRAFFIC_BYTES = 1155725312 + 126750976
 METRIC = "fused bf16 GEMM+bias+GELU TFLOP/s via pyc_cuda_dispatch"
 
 
@@ -590,6 +590,21 @@ def run_only(args):
         rs, cs, d = torch.ones(m, device="cuda"), torch.ones(n, device="cuda"), torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
         run = lambda: backend.gemm_fp8(m, n, k, a.data_ptr(), b.data_ptr(), d.data_ptr(), rs.data_ptr(), cs.data_ptr(), None, abi.ACT_GELU)
         work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+    elif args.only == "ffn":
+        from pyc_b200 import ffn
+        tokens, hidden, inner = dims or [2048, 4096, 16384]
+        x = rnd((tokens, hidden))
+
+        def fp8_weight(k, n):
+            w = torch.randn((k, n), generator=g, device="cuda") * k ** -0.5
+            scale = (w.abs().amax(dim=0) / 448.0).clamp_min(1e-30)
+            return (w / scale).to(torch.float8_e4m3fn).view(torch.uint8).cpu().numpy(), scale.float().cpu().numpy()
+        w1, s1 = fp8_weight(hidden, inner)
+        w2, s2 = fp8_weight(inner, hidden)
+        blk = ffn.FfnBlock(tokens, hidden, inner, w1, s1, w2, s2, torch, single=True)
+        xb = x.view(torch.int16)
+        run = lambda: blk.run(xb)
+        work, unit = 4.0 * tokens * hidden * inner / 1e12, "TFLOP/s"
     else:
         raise SystemExit(f"--only {args.only}: unknown kernel")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
@@ -611,8 +626,8 @@ def run_only(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default=None, help="gemm | attention | conv2d | add | bias_gelu | layernorm | softmax | gemm_fp8: one kernel, for profilers")
-    ap.add_argument("--shape", default=None, help="--only: comma-separated sizes (gemm M,N,K; attention heads,seq,d; conv2d N,H,C,K; rows,cols)")
+    ap.add_argument("--only", default=None, help="gemm | attention | conv2d | add | bias_gelu | layernorm | softmax | gemm_fp8 | ffn: one kernel (ffn: the four launches of one block), for profilers")
+    ap.add_argument("--shape", default=None, help="--only: comma-separated sizes (gemm M,N,K; attention heads,seq,d; conv2d N,H,C,K; rows,cols; ffn tokens,hidden,inner)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16", "f32"])
     ap.add_argument("--epilogue", default="bias_gelu", choices=["none", "bias_relu", "bias_gelu"])
     ap.add_argument("--symbol", default=None)
