@@ -251,6 +251,119 @@ gemm_simt_latency_kernel(SimtParams p) {
     *reinterpret_cast<float4*>(D + static_cast<size_t>(r) * N + c0) = make_float4(v[0], v[1], v[2], v[3]);
 }
 
+// Throughput variant for large fp32 problems: 128 x 128 x 8 tile, 256 threads, 8 x 8 outputs per thread, two CTAs per SM,
+// and the FMAs issued as packed pairs (fma.rn.f32x2: two independent IEEE fp32 FMAs per instruction, so half the issue
+// slots; each lane is bit-identical to fmaf).  What bounds an fp32 GEMM on this SM is the shared-memory return path
+// (128 bytes per clock): a thread with a TM x TN register tile reads (TM + TN) * 4 bytes per TM * TN FMAs, so the
+// 4 x 4 tile of the kernel above can feed only half of the 128 FMA lanes and an 8 x 8 tile just feeds all of them.
+// Neither operand is stored twice to make the pairs: a pair of accumulators holds a DIAGONAL of a 2 x 2 block,
+//   P = {C[i][j], C[i+1][j+1]} += {a_i, a_i+1} * {b_j, b_j+1},    Q = {C[i][j+1], C[i+1][j]} += {a_i, a_i+1} * {b_j+1, b_j},
+// so A pairs come straight out of a 16-byte read of the transposed A tile and B needs one swapped copy in registers.
+// Needs row-major B, K % 4 == 0, N % 4 == 0 and 16-byte aligned A, B and D.  k ascends, one accumulator per output.
+constexpr int XBM = 128, XBN = 128, XBK = 8, XTHREADS = 256, XA_STRIDE = XBM + 16;
+
+__device__ __forceinline__ void ffma2(unsigned long long& d, unsigned long long a, unsigned long long b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+__global__ void __launch_bounds__(XTHREADS, 2)
+gemm_simt_x2_kernel(SimtParams p) {
+    __shared__ __align__(16) float As[2][XBK][XA_STRIDE];   // [k][m]: transposed on the way in
+    __shared__ __align__(16) float Bs[2][XBK][XBN];
+    const float* __restrict__ A = reinterpret_cast<const float*>(p.A);
+    const float* __restrict__ B = reinterpret_cast<const float*>(p.B);
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * XBM, n0 = blockIdx.x * XBN;
+    const int M = p.M, N = p.N, K = p.K;
+    // One float4 of each operand per thread and k-slice: A row tid/2, k-chunk tid%2; B k-row tid/32, columns (tid%32)*4.
+    const int a_row = tid >> 1, a_kc = (tid & 1) * 4;
+    const int b_row = tid >> 5, b_nc = (tid & 31) * 4;
+    float4 ra, rb;
+    auto fetch = [&](int k0) {
+        const bool oka = (m0 + a_row) < M && (k0 + a_kc) < K;
+        ra = oka ? __ldg(reinterpret_cast<const float4*>(A + static_cast<size_t>(m0 + a_row) * K + k0 + a_kc)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const bool okb = (k0 + b_row) < K && (n0 + b_nc) < N;
+        rb = okb ? __ldg(reinterpret_cast<const float4*>(B + static_cast<size_t>(k0 + b_row) * N + n0 + b_nc)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    auto stash = [&](int buf) {
+        As[buf][a_kc + 0][a_row] = ra.x; As[buf][a_kc + 1][a_row] = ra.y;
+        As[buf][a_kc + 2][a_row] = ra.z; As[buf][a_kc + 3][a_row] = ra.w;
+        *reinterpret_cast<float4*>(&Bs[buf][b_row][b_nc]) = rb;
+    };
+
+    unsigned long long P[4][4], Q[4][4];   // row pair ip = rows (ip/2)*64 + ty*4 + (ip%2)*2 + {0,1}; column pair jp = (jp/2)*64 + tx*4 + (jp%2)*2 + {0,1}
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { P[i][j] = 0ull; Q[i][j] = 0ull; }
+
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int k0 = 0; k0 < K; k0 += XBK) {
+        const bool more = k0 + XBK < K;
+        if (more) fetch(k0 + XBK);
+#pragma unroll
+        for (int kk = 0; kk < XBK; ++kk) {
+            unsigned long long ap[4], bp[4], bs[4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(&As[buf][kk][h * 64 + ty * 4]);
+                ap[h * 2] = v.x; ap[h * 2 + 1] = v.y;
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float4 v = *reinterpret_cast<const float4*>(&Bs[buf][kk][h * 64 + tx * 4]);
+                bp[h * 2] = pack2(v.x, v.y); bp[h * 2 + 1] = pack2(v.z, v.w);
+                bs[h * 2] = pack2(v.y, v.x); bs[h * 2 + 1] = pack2(v.w, v.z);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { ffma2(P[i][j], ap[i], bp[j]); ffma2(Q[i][j], ap[i], bs[j]); }
+        }
+        if (more) { stash(buf ^ 1); __syncthreads(); buf ^= 1; }
+    }
+
+    float* D = reinterpret_cast<float*>(p.D);
+    const float* add = reinterpret_cast<const float*>(p.add);
+    const float sadd = p.add_mode == PYC_B200_ADD_SCALAR ? p.add_scale * __ldg(add) : 0.0f;
+#pragma unroll
+    for (int ip = 0; ip < 4; ++ip) {
+        const int r0 = m0 + (ip >> 1) * 64 + ty * 4 + (ip & 1) * 2;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int c0 = n0 + h * 64 + tx * 4;
+            if (c0 >= N) continue;              // N % 4 == 0: a thread's four columns are in or out together
+            float v[2][4];
+            unpack2(P[ip][h * 2], v[0][0], v[1][1]);     unpack2(Q[ip][h * 2], v[0][1], v[1][0]);
+            unpack2(P[ip][h * 2 + 1], v[0][2], v[1][3]); unpack2(Q[ip][h * 2 + 1], v[0][3], v[1][2]);
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int r = r0 + rr;
+                if (r >= M) continue;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float o = p.alpha * v[rr][j] + sadd;
+                    if (p.add_mode == PYC_B200_ADD_ROW_BIAS) o += p.add_scale * __ldg(add + c0 + j);
+                    else if (p.add_mode == PYC_B200_ADD_MATRIX) o += p.add_scale * __ldg(add + static_cast<size_t>(r) * N + c0 + j);
+                    v[rr][j] = act_fn(o, p.act);
+                }
+                *reinterpret_cast<float4*>(D + static_cast<size_t>(r) * N + c0) = make_float4(v[rr][0], v[rr][1], v[rr][2], v[rr][3]);
+            }
+        }
+    }
+}
+
 template <typename T, int BM, int BN, int TM, int TN>
 int launch_one(const SimtParams& sp, cudaStream_t stream) {
     dim3 grid((sp.N + BN - 1) / BN, (sp.M + BM - 1) / BM);
@@ -268,6 +381,14 @@ bool latency_kernel_ok(const SimtParams& sp) {
 template <typename T>
 int launch_typed(const GemmConfig& cfg, const SimtParams& sp, cudaStream_t stream) {
     if constexpr (std::is_same<T, float>::value) {
+        if (cfg.bm == XBM && cfg.bn == XBN && cfg.bk == XBK) {
+            if (!latency_kernel_ok(sp)) { set_error("simt_x2_128x128x8 needs row-major B, K %% 4 == 0, N %% 4 == 0 and 16-byte aligned pointers"); return -1; }
+            dim3 grid((sp.N + XBN - 1) / XBN, (sp.M + XBM - 1) / XBM);
+            gemm_simt_x2_kernel<<<grid, XTHREADS, 0, stream>>>(sp);
+            B200_CUDA_OK(cudaGetLastError());
+            count_launch();
+            return 0;
+        }
         if (cfg.bm == 32 && cfg.bn == 64 && cfg.bk == 32) {
             if (!latency_kernel_ok(sp)) { set_error("simt_async_32x64x32 needs row-major B, K %% 4 == 0, N %% 4 == 0 and 16-byte aligned pointers"); return -1; }
             dim3 grid((sp.N + LBN - 1) / LBN, (sp.M + LBM - 1) / LBM);

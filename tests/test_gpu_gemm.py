@@ -98,6 +98,33 @@ def test_simt_latency_tile_f32(backend, oracle_lib):
         run_case(backend, oracle_lib, abi.DTYPE_F32, 16, 16, 18, cfg=cfg, seed=25)
 
 
+def test_simt_packed_fma_tile_f32(backend, oracle_lib):
+    cfg = "simt_x2_128x128x8"
+    run_case(backend, oracle_lib, abi.DTYPE_F32, 512, 512, 512, cfg=cfg, add_mode=abi.ADD_ROW_BIAS, act=abi.ACT_RELU, seed=31)
+    run_case(backend, oracle_lib, abi.DTYPE_F32, 130, 100, 72, cfg=cfg, add_mode=abi.ADD_MATRIX, act=abi.ACT_GELU, seed=32)   # ragged in M, N and K
+    run_case(backend, oracle_lib, abi.DTYPE_F32, 33, 20, 68, cfg=cfg, add_mode=abi.ADD_SCALAR, alpha=0.5, seed=33)
+    run_case(backend, oracle_lib, abi.DTYPE_F32, 1, 4, 4, cfg=cfg, seed=34)
+    run_case(backend, oracle_lib, abi.DTYPE_F32, 1024, 516, 1280, cfg=cfg, seed=35)     # several tiles per CTA slot, K % 8 != 0
+    with pytest.raises(backend.BackendError):   # N % 4 != 0 is not this tile's business
+        run_case(backend, oracle_lib, abi.DTYPE_F32, 16, 16, 18, cfg=cfg, seed=36)
+
+
+def test_simt_packed_fma_is_bit_identical_to_the_scalar_fma_kernel(backend):
+    # fma.rn.f32x2 is two independent IEEE FMAs and both kernels accumulate in ascending k with one accumulator per output.
+    from gpu_util import empty_device, sync_ok, to_device
+    M, K, N = 300, 516, 260
+    a = workloads.normal((M, K), 41, 1.0); b = workloads.normal((K, N), 42, 1.0); bias = workloads.normal((N,), 43, 1.0)
+    d_a, d_b, d_c = to_device(a), to_device(b), to_device(bias)
+    outs = []
+    for cfg in ("simt_x2_128x128x8", "simt_64x64x16"):
+        d_o = empty_device(abi.DTYPE_F32, (M, N))
+        backend.gemm(abi.DTYPE_F32, M, N, K, d_a.data_ptr(), d_b.data_ptr(), d_o.data_ptr(), add=d_c.data_ptr(),
+                     add_mode=abi.ADD_ROW_BIAS, act=abi.ACT_RELU, symbol=f"b200_gemm_f32_{cfg}")
+        sync_ok()
+        outs.append(d_o.cpu().numpy())
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+
+
 def test_config1_f32_512_matches_golden_definition(backend, oracle_lib):
     # benchmark configuration 1: X[512,512] W[512,512] b[512] ~ U(-1,1), matmul -> add -> relu.
     from gpu_util import empty_device, rel_err, sync_ok, to_device
