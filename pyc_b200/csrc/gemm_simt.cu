@@ -12,6 +12,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "internal.h"
@@ -251,17 +252,26 @@ gemm_simt_latency_kernel(SimtParams p) {
     *reinterpret_cast<float4*>(D + static_cast<size_t>(r) * N + c0) = make_float4(v[0], v[1], v[2], v[3]);
 }
 
-// Throughput variant for large fp32 problems: 128 x 128 x 8 tile, 256 threads, 8 x 8 outputs per thread, two CTAs per SM,
+// Throughput variant for large fp32 problems: 128 x 128 x 32 tile, 256 threads, 8 x 8 outputs per thread, two CTAs per SM,
 // and the FMAs issued as packed pairs (fma.rn.f32x2: two independent IEEE fp32 FMAs per instruction, so half the issue
-// slots; each lane is bit-identical to fmaf).  What bounds an fp32 GEMM on this SM is the shared-memory return path
-// (128 bytes per clock): a thread with a TM x TN register tile reads (TM + TN) * 4 bytes per TM * TN FMAs, so the
-// 4 x 4 tile of the kernel above can feed only half of the 128 FMA lanes and an 8 x 8 tile just feeds all of them.
+// slots; each lane is bit-identical to fmaf).  What bounds an fp32 GEMM on this SM next to the FMA pipe is the
+// shared-memory return path (128 bytes per clock): a thread with a TM x TN register tile reads (TM + TN) * 4 bytes per
+// TM * TN FMAs, so a 4 x 4 tile can feed only half of the 128 FMA lanes and an 8 x 8 tile just feeds all of them.
 // Neither operand is stored twice to make the pairs: a pair of accumulators holds a DIAGONAL of a 2 x 2 block,
 //   P = {C[i][j], C[i+1][j+1]} += {a_i, a_i+1} * {b_j, b_j+1},    Q = {C[i][j+1], C[i+1][j]} += {a_i, a_i+1} * {b_j+1, b_j},
 // so A pairs come straight out of a 16-byte read of the transposed A tile and B needs one swapped copy in registers.
-// Needs row-major B, K % 4 == 0, N % 4 == 0 and 16-byte aligned A, B and D.  k ascends, one accumulator per output.
-constexpr int XBM = 128, XBN = 128, XBK = 8, XTHREADS = 256, XA_STRIDE = XBM + 16;
+// Operands arrive by cp.async into a two-slot ring of 32-deep k-slices (one barrier per 32 k-steps; 8-deep slices cost
+// 7 % in barriers): A element by element, which is what transposes it ([k][m], row stride 132 floats: the 8 k x 4 rows a
+// warp copies per instruction are 4 full 32-byte sectors in global memory and 32 different banks in shared memory),
+// B in 16-byte pieces.  Needs row-major B, N % 4 == 0 and 16-byte aligned B and D.  k ascends, one accumulator per output.
+constexpr int XBM = 128, XBN = 128, XBK = 32, XSTAGES = 2, XTHREADS = 256, XA_STRIDE = XBM + 4;
+constexpr int X_SMEM_BYTES = XSTAGES * XBK * (XA_STRIDE + XBN) * 4;
 
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem, bool valid) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const int bytes = valid ? 4 : 0;   // 0 source bytes: the destination is zero-filled
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gmem), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void ffma2(unsigned long long& d, unsigned long long a, unsigned long long b) {
     asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
 }
@@ -276,53 +286,60 @@ __device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& 
 
 __global__ void __launch_bounds__(XTHREADS, 2)
 gemm_simt_x2_kernel(SimtParams p) {
-    __shared__ __align__(16) float As[2][XBK][XA_STRIDE];   // [k][m]: transposed on the way in
-    __shared__ __align__(16) float Bs[2][XBK][XBN];
+    extern __shared__ __align__(16) float x_smem[];
+    float (*As)[XBK][XA_STRIDE] = reinterpret_cast<float (*)[XBK][XA_STRIDE]>(x_smem);               // [slot][k][m]
+    float (*Bs)[XBK][XBN] = reinterpret_cast<float (*)[XBK][XBN]>(x_smem + XSTAGES * XBK * XA_STRIDE);   // [slot][k][n]
     const float* __restrict__ A = reinterpret_cast<const float*>(p.A);
     const float* __restrict__ B = reinterpret_cast<const float*>(p.B);
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * XBM, n0 = blockIdx.x * XBN;
     const int M = p.M, N = p.N, K = p.K;
-    // One float4 of each operand per thread and k-slice: A row tid/2, k-chunk tid%2; B k-row tid/32, columns (tid%32)*4.
-    const int a_row = tid >> 1, a_kc = (tid & 1) * 4;
-    const int b_row = tid >> 5, b_nc = (tid & 31) * 4;
-    float4 ra, rb;
-    auto fetch = [&](int k0) {
-        const bool oka = (m0 + a_row) < M && (k0 + a_kc) < K;
-        ra = oka ? __ldg(reinterpret_cast<const float4*>(A + static_cast<size_t>(m0 + a_row) * K + k0 + a_kc)) : make_float4(0.f, 0.f, 0.f, 0.f);
-        const bool okb = (k0 + b_row) < K && (n0 + b_nc) < N;
-        rb = okb ? __ldg(reinterpret_cast<const float4*>(B + static_cast<size_t>(k0 + b_row) * N + n0 + b_nc)) : make_float4(0.f, 0.f, 0.f, 0.f);
-    };
-    auto stash = [&](int buf) {
-        As[buf][a_kc + 0][a_row] = ra.x; As[buf][a_kc + 1][a_row] = ra.y;
-        As[buf][a_kc + 2][a_row] = ra.z; As[buf][a_kc + 3][a_row] = ra.w;
-        *reinterpret_cast<float4*>(&Bs[buf][b_row][b_nc]) = rb;
+    const int steps = (K + XBK - 1) / XBK;
+    const int a_k = tid & 7, a_row = tid >> 3;           // A: k = a_k + 8q, rows a_row + 32i
+    const int b_row = tid >> 5, b_nc = (tid & 31) * 4;   // B: k-rows b_row + 8i, four columns from b_nc
+
+    auto issue = [&](int step, int slot) {
+        const int k0 = step * XBK;
+#pragma unroll
+        for (int i = 0; i < XBK / 2; ++i) {
+            const int r = a_row + 32 * (i / (XBK / 8)), kq = a_k + 8 * (i % (XBK / 8));
+            const bool ok = (m0 + r) < M && (k0 + kq) < K;
+            cp_async4(&As[slot][kq][r], ok ? A + static_cast<size_t>(m0 + r) * K + k0 + kq : A, ok);
+        }
+#pragma unroll
+        for (int i = 0; i < XBK / 8; ++i) {
+            const int br = b_row + 8 * i;
+            const bool ok = (k0 + br) < K && (n0 + b_nc) < N;
+            cp_async16(&Bs[slot][br][b_nc], ok ? B + static_cast<size_t>(k0 + br) * N + n0 + b_nc : B, ok);
+        }
     };
 
-    unsigned long long P[4][4], Q[4][4];   // row pair ip = rows (ip/2)*64 + ty*4 + (ip%2)*2 + {0,1}; column pair jp = (jp/2)*64 + tx*4 + (jp%2)*2 + {0,1}
+    unsigned long long P[4][4], Q[4][4];   // row pair ip: rows (ip/2)*64 + ty*4 + (ip%2)*2 + {0,1}; column pair jp: (jp/2)*64 + tx*4 + (jp%2)*2 + {0,1}
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) { P[i][j] = 0ull; Q[i][j] = 0ull; }
 
-    fetch(0);
-    stash(0);
-    __syncthreads();
-    int buf = 0;
-    for (int k0 = 0; k0 < K; k0 += XBK) {
-        const bool more = k0 + XBK < K;
-        if (more) fetch(k0 + XBK);
+#pragma unroll
+    for (int s = 0; s < XSTAGES - 1; ++s) { if (s < steps) issue(s, s); cp_async_commit(); }
+    for (int step = 0; step < steps; ++step) {
+        cp_async_wait<XSTAGES - 2>();
+        __syncthreads();                       // slice `step` has landed for everyone; the slot refilled below was read last step
+        const int nxt = step + XSTAGES - 1;
+        if (nxt < steps) issue(nxt, nxt % XSTAGES);
+        cp_async_commit();
+        const int slot = step % XSTAGES;
 #pragma unroll
         for (int kk = 0; kk < XBK; ++kk) {
             unsigned long long ap[4], bp[4], bs[4];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(&As[buf][kk][h * 64 + ty * 4]);
+                const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(&As[slot][kk][h * 64 + ty * 4]);
                 ap[h * 2] = v.x; ap[h * 2 + 1] = v.y;
             }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const float4 v = *reinterpret_cast<const float4*>(&Bs[buf][kk][h * 64 + tx * 4]);
+                const float4 v = *reinterpret_cast<const float4*>(&Bs[slot][kk][h * 64 + tx * 4]);
                 bp[h * 2] = pack2(v.x, v.y); bp[h * 2 + 1] = pack2(v.z, v.w);
                 bs[h * 2] = pack2(v.y, v.x); bs[h * 2 + 1] = pack2(v.w, v.z);
             }
@@ -331,7 +348,6 @@ gemm_simt_x2_kernel(SimtParams p) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) { ffma2(P[i][j], ap[i], bp[j]); ffma2(Q[i][j], ap[i], bs[j]); }
         }
-        if (more) { stash(buf ^ 1); __syncthreads(); buf ^= 1; }
     }
 
     float* D = reinterpret_cast<float*>(p.D);
@@ -382,9 +398,16 @@ template <typename T>
 int launch_typed(const GemmConfig& cfg, const SimtParams& sp, cudaStream_t stream) {
     if constexpr (std::is_same<T, float>::value) {
         if (cfg.bm == XBM && cfg.bn == XBN && cfg.bk == XBK) {
-            if (!latency_kernel_ok(sp)) { set_error("simt_x2_128x128x8 needs row-major B, K %% 4 == 0, N %% 4 == 0 and 16-byte aligned pointers"); return -1; }
+            if (!latency_kernel_ok(sp)) { set_error("simt_x2_128x128x32 needs row-major B, K %% 4 == 0, N %% 4 == 0 and 16-byte aligned pointers"); return -1; }
+            static std::atomic<bool> opted_in[64];   // the opt-in for more than 48 KB of dynamic shared memory is per device
+            int dev = 0;
+            B200_CUDA_OK(cudaGetDevice(&dev));
+            if (dev < 0 || dev >= 64 || !opted_in[dev].load(std::memory_order_acquire)) {
+                B200_CUDA_OK(cudaFuncSetAttribute(gemm_simt_x2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, X_SMEM_BYTES));
+                if (dev >= 0 && dev < 64) opted_in[dev].store(true, std::memory_order_release);
+            }
             dim3 grid((sp.N + XBN - 1) / XBN, (sp.M + XBM - 1) / XBM);
-            gemm_simt_x2_kernel<<<grid, XTHREADS, 0, stream>>>(sp);
+            gemm_simt_x2_kernel<<<grid, XTHREADS, X_SMEM_BYTES, stream>>>(sp);
             B200_CUDA_OK(cudaGetLastError());
             count_launch();
             return 0;

@@ -247,7 +247,7 @@ static const GemmConfig kGemmConfigs[] = {
     {"tc_128x256x64_s4", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 256, 64, 4, 100, 197744, PYC_KERNEL_WORKLOAD_SQUARE},
     {"tc_128x128x64_s6", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 128, 64, 6, 100, 197776, PYC_KERNEL_WORKLOAD_TALL_SKINNY},
     {"tc_128x64x64_s8", GEMM_TC, (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 64, 64, 8, 100, 197808, PYC_KERNEL_WORKLOAD_SMALL},
-    {"simt_x2_128x128x8", GEMM_SIMT, (1 << PYC_DTYPE_F32), 128, 128, 8, 2, 30, 17408, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
+    {"simt_x2_128x128x32", GEMM_SIMT, (1 << PYC_DTYPE_F32), 128, 128, 32, 2, 30, 66560, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
     {"simt_128x128x16", GEMM_SIMT, (1 << PYC_DTYPE_F32) | (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 128, 128, 16, 2, 30, 33792, PYC_KERNEL_WORKLOAD_LARGE_SQUARE},
     {"simt_64x64x16", GEMM_SIMT, (1 << PYC_DTYPE_F32) | (1 << PYC_DTYPE_BF16) | (1 << PYC_DTYPE_F16), 64, 64, 16, 2, 30, 17408, PYC_KERNEL_WORKLOAD_SQUARE},
     {"simt_async_32x64x32", GEMM_SIMT, (1 << PYC_DTYPE_F32), 32, 64, 32, 3, 30, 38400, PYC_KERNEL_WORKLOAD_SMALL},
@@ -336,7 +336,7 @@ static void registry_fill_locked() {
             // PyC adds 6 x estimated occupancy to a score and breaks exact ties by symbol name: the packed-FMA tile gets
             // a slightly higher estimate than the scalar tile of the same shape, priority and workload family, so that it
             // is the one proposed for large fp32 problems (when it cannot take a problem the next check falls through).
-            const double occ = c.kind != GEMM_SIMT ? 0.09 : c.bk == 8 ? 0.55 : 0.5;
+            const double occ = c.kind != GEMM_SIMT ? 0.09 : (c.bm == 128 && c.bk == 32) ? 0.55 : 0.5;
             reg_add("matmul", gemm_symbol(d, c), prio, occ, c.kind != GEMM_SIMT ? 1 : 0, c.smem_bytes,
                     c.kind != GEMM_SIMT ? 2 : 1, c.workload);
             // The same descriptor under a dtype-qualified key: PyC's selection returns ONE winner per op key, and a
@@ -445,7 +445,7 @@ void remember_gemm_winner(pyc_dtype dtype, int M, int N, int K, const GemmConfig
 bool gemm_config_supports(const GemmConfig& cfg, const GemmProblem& p) {
     if (!(cfg.dtype_mask & (1 << p.dtype))) return false;
     if (cfg.kind == GEMM_SIMT) {
-        if (cfg.bk == 32 || cfg.bk == 8)  // the cp.async latency tile and the packed-FMA tile: 16-byte loads of row-major operands
+        if (cfg.bk == 32)  // the cp.async tiles (latency tile, packed-FMA tile): 16-byte loads of row-major operands
             return !p.b_col_major && p.K % 4 == 0 && p.N % 4 == 0 && reinterpret_cast<uintptr_t>(p.A) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(p.B) % 16 == 0 && reinterpret_cast<uintptr_t>(p.D) % 16 == 0;
         return true;
@@ -468,7 +468,7 @@ static double model_cost(const GemmConfig& c, const GemmProblem& p, int sms) {
     double eff, slots;
     if (c.kind == GEMM_TC) { eff = c.bn == 256 ? 1.0 : c.bn == 128 ? 0.85 : 0.6; slots = sms; }
     else if (c.kind == GEMM_TC_PAIR) { eff = kPairEfficiency; slots = sms / 2; }
-    else { eff = (c.bk == 8 ? 2.3 : c.bm == 128 ? 1.0 : c.bm == 64 ? 0.8 : c.bk == 32 ? 0.75 : 0.55) / 24.0; slots = sms * (c.bm == 128 ? 2.0 : 4.0); }  // packed-FMA tile: 44 TFLOP/s measured against 30 for 64 x 64
+    else { eff = ((c.bm == 128 && c.bk == 32) ? 2.7 : c.bm == 128 ? 1.0 : c.bm == 64 ? 0.8 : c.bk == 32 ? 0.75 : 0.55) / 24.0; slots = sms * (c.bm == 128 ? 2.0 : 4.0); }  // packed-FMA tile: 51 TFLOP/s measured against 30 for 64 x 64
     const double waves = static_cast<double>(static_cast<long long>((tiles + slots - 1) / slots));
     return waves * c.bm * c.bn / eff / (c.kind == GEMM_TC_PAIR ? 2.0 : 1.0);  // a pair tile is the work of two SMs
 }

@@ -73,7 +73,7 @@ def test_pyc_scoring_picks_the_tile_meant_for_each_workload_family(front):
     assert _select(front, "matmul.bf16", SMALL) == "b200_gemm_bf16_tc_128x64x64_s8"
     assert _select(front, "matmul.f16", LARGE_SQUARE) == "b200_gemm_f16_tc2_256x256x64_s6"
     assert _select(front, "matmul.f32", SMALL) == "b200_gemm_f32_simt_async_32x64x32"
-    assert _select(front, "matmul.f32", LARGE_SQUARE) == "b200_gemm_f32_simt_x2_128x128x8"
+    assert _select(front, "matmul.f32", LARGE_SQUARE) == "b200_gemm_f32_simt_x2_128x128x32"
     # Tensor-core tiles share one priority, so once every candidate has been timed (PyC scores -100 per measured ms and
     # nothing for an untimed kernel) the measured times decide, here between the two CTA-pair variants.
     times = {"tc2_256x256x64_s6": 0.80, "tc2_256x256x64_s7": 0.75, "tc_128x256x64_s4": 0.82, "tc_128x128x64_s6": 0.95, "tc_128x64x64_s8": 1.30,

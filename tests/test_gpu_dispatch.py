@@ -77,6 +77,19 @@ def test_matmul_chains(backend, oracle_lib, device, dtype, tol, bias, act):
     assert trace.reason.decode().startswith("b200_graph_")
 
 
+def test_large_f32_module_is_planned_on_the_packed_fma_tile_and_replays(backend, oracle_lib):
+    # large enough for the wave model to prefer the 128 x 128 fp32 tile; first call captures the graph (with the kernel's
+    # shared-memory opt-in inside the capture), second replays it
+    from gpu_util import rel_err
+    M, K, N = 2048, 384, 2304
+    mod = ir.matmul_bias_act(abi.DTYPE_F32, M, K, N, bias="row", act="gelu")
+    arrays = [workloads.normal((M, K), 81, 0.5), workloads.normal((K, N), 82, 0.5), workloads.normal((N,), 83, 2.0)]
+    for want_reason in ("b200_graph_capture:", "b200_graph_replay:"):
+        got, want, trace = run_module_both(backend, oracle_lib, mod, arrays, abi.DTYPE_F32, (M, N), True)
+        assert rel_err(got, want) <= 1e-5
+        assert trace.reason.decode() == want_reason + "b200_gemm_f32_simt_x2_128x128x32"
+
+
 @pytest.mark.parametrize("dtype,tol", [(abi.DTYPE_F32, 1e-5), (abi.DTYPE_BF16, 2e-2)])
 def test_ffn_like_module_with_arena_reuse(backend, oracle_lib, dtype, tol):
     # layernorm -> matmul -> +bias -> gelu -> matmul -> +bias -> (+ residual) -> reduce_sum as second output

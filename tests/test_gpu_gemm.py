@@ -99,7 +99,7 @@ def test_simt_latency_tile_f32(backend, oracle_lib):
 
 
 def test_simt_packed_fma_tile_f32(backend, oracle_lib):
-    cfg = "simt_x2_128x128x8"
+    cfg = "simt_x2_128x128x32"
     run_case(backend, oracle_lib, abi.DTYPE_F32, 512, 512, 512, cfg=cfg, add_mode=abi.ADD_ROW_BIAS, act=abi.ACT_RELU, seed=31)
     run_case(backend, oracle_lib, abi.DTYPE_F32, 130, 100, 72, cfg=cfg, add_mode=abi.ADD_MATRIX, act=abi.ACT_GELU, seed=32)   # ragged in M, N and K
     run_case(backend, oracle_lib, abi.DTYPE_F32, 33, 20, 68, cfg=cfg, add_mode=abi.ADD_SCALAR, alpha=0.5, seed=33)
@@ -116,7 +116,7 @@ def test_simt_packed_fma_is_bit_identical_to_the_scalar_fma_kernel(backend):
     a = workloads.normal((M, K), 41, 1.0); b = workloads.normal((K, N), 42, 1.0); bias = workloads.normal((N,), 43, 1.0)
     d_a, d_b, d_c = to_device(a), to_device(b), to_device(bias)
     outs = []
-    for cfg in ("simt_x2_128x128x8", "simt_64x64x16"):
+    for cfg in ("simt_x2_128x128x32", "simt_64x64x16"):
         d_o = empty_device(abi.DTYPE_F32, (M, N))
         backend.gemm(abi.DTYPE_F32, M, N, K, d_a.data_ptr(), d_b.data_ptr(), d_o.data_ptr(), add=d_c.data_ptr(),
                      add_mode=abi.ADD_ROW_BIAS, act=abi.ACT_RELU, symbol=f"b200_gemm_f32_{cfg}")
