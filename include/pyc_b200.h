@@ -254,6 +254,23 @@ int pyc_b200_ffn_block_scatter(const pyc_b200_ffn_args* args, void* workspace, s
                                int world, int rank, void* stream);
 int pyc_b200_tp_reduce_broadcast(const void* recv_local, void* const* outs, int world, int rank, int rows_per_rank, int hidden,
                                  void* stream);
+/* All-reduce (sum) of a [rows][hidden] bf16 tensor inside the NVSwitch, for the tensor-parallel FFN's partial sums: the
+ * third way to do the exchange that pyc_b200_ffn_block_tp does through comm->all_reduce (include/pyc/collective_comm.h:49-58).
+ * Every rank's copy of the tensor sits at the same offset of a buffer bound to ONE NVLink multicast object (cuMulticast*;
+ * torch.distributed._symmetric_memory does the allocation and hands out the address) and `multicast_ptr` is the multicast
+ * address of the tensor.  Each rank reduces 1/world of the 16-byte pieces with multimem.ld_reduce (fp32 accumulation in
+ * the switch, one rounding) and broadcasts them with multimem.st; in place, on `stream`, one kernel of
+ * PYC_B200_TP_MULTIMEM_BLOCKS blocks that must be co-resident (nothing else may hold the GPU's SMs for long).
+ *   flag_ptrs[r]   : rank r's flag words, PYC_B200_TP_MULTIMEM_BLOCKS * PYC_B200_TP_MAX_RANKS uint32, zeroed once before the
+ *                    first call, writable from every rank (own pointer at [rank], peer mappings elsewhere);
+ *   epoch_counters : PYC_B200_TP_MULTIMEM_BLOCKS uint32 in local device memory, zeroed once; the kernel advances them, so the
+ *                    call can be captured in a CUDA graph and replayed.
+ * Every rank must make the same sequence of calls.  The two cross-GPU rendezvous inside the kernel are bounded waits
+ * (~2 s); one that runs out shows as ((40 | 41) << 8) | 1 in pyc_b200_device_status().  The producer of the partial sums
+ * must be earlier work on the same stream.  PyC has no counterpart (its NCCL shim calls ncclAllReduce). */
+#define PYC_B200_TP_MULTIMEM_BLOCKS 128
+int pyc_b200_tp_allreduce_multimem(void* multicast_ptr, void* const* flag_ptrs, void* epoch_counters, int world, int rank,
+                                   size_t rows, size_t hidden, void* stream);
 /* Device memory that other processes on the same node can map: allocate + export a 64-byte handle, open a peer's handle,
  * close it again, free the own allocation.  (cudaMalloc + CUDA IPC; the handle is sent by whatever channel the caller has.) */
 int pyc_b200_symm_alloc(size_t bytes, void** ptr, unsigned char handle[64]);

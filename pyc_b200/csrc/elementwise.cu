@@ -132,32 +132,56 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, 
 }
 
 // Row bias (+ activation): every thread owns one 16-byte column slot, keeps its slice of the bias in registers and
-// walks down the rows, so there is no index arithmetic beyond one add per row.
+// walks down the rows, so there is no index arithmetic beyond one add per row.  The next group of rows is fetched as raw
+// 16-byte words before the current group is converted and computed: with GELU on a 2-byte type the arithmetic of a group
+// is as long as its memory time, and without the prefetch a warp has no load in flight while it computes.
+template <typename T, int VEC>
+__device__ __forceinline__ void unpack_vec(const uint4& raw, float (&f)[VEC]) {
+    union { uint4 u; T t[VEC]; } x;
+    x.u = raw;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) f[i] = to_f(x.t[i]);
+}
+
 template <typename T, int VEC, int ACT>
 __global__ void __launch_bounds__(256) row_bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ out,
                                                           size_t rows, size_t cols) {
+    static_assert(VEC * sizeof(T) == 16, "one 16-byte slot per thread");
     const size_t vec_per_row = cols / VEC;
     const size_t col_vec = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (col_vec >= vec_per_row) return;
     float b[VEC];
     load_vec<T, VEC>(bias + col_vec * VEC, b);
     constexpr int UNROLL = 4;
-    for (size_t r0 = blockIdx.y; r0 < rows; r0 += static_cast<size_t>(gridDim.y) * UNROLL) {
-        float v[UNROLL][VEC];
+    const size_t step = static_cast<size_t>(gridDim.y);
+    const T* xp = x + col_vec * VEC;
+    T* op = out + col_vec * VEC;
+    uint4 cur[UNROLL], nxt[UNROLL];
+    auto fetch = [&](size_t r0, uint4 (&dst)[UNROLL]) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const size_t r = r0 + static_cast<size_t>(u) * gridDim.y;
-            if (r < rows) load_vec<T, VEC>(x + r * cols + col_vec * VEC, v[u]);
+            const size_t r = r0 + static_cast<size_t>(u) * step;
+            if (r < rows) dst[u] = __ldg(reinterpret_cast<const uint4*>(xp + r * cols));
         }
+    };
+    size_t r0 = blockIdx.y;
+    if (r0 < rows) fetch(r0, cur);
+    for (; r0 < rows; r0 += step * UNROLL) {
+        const size_t rn = r0 + step * UNROLL;
+        if (rn < rows) fetch(rn, nxt);
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const size_t r = r0 + static_cast<size_t>(u) * gridDim.y;
+            const size_t r = r0 + static_cast<size_t>(u) * step;
             if (r >= rows) continue;
+            float v[VEC];
+            unpack_vec<T, VEC>(cur[u], v);
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) v[u][j] += b[j];
-            act_vec<ACT, VEC>(v[u]);
-            store_vec<T, VEC>(out + r * cols + col_vec * VEC, v[u]);
+            for (int j = 0; j < VEC; ++j) v[j] += b[j];
+            act_vec<ACT, VEC>(v);
+            store_vec<T, VEC>(op + r * cols, v);
         }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) cur[u] = nxt[u];
     }
 }
 

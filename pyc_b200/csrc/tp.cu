@@ -42,10 +42,104 @@ __global__ void __launch_bounds__(256) tp_reduce_broadcast_kernel(ReduceArgs a) 
     }
 }
 
+// ---- all-reduce inside the NVSwitch (multimem) ---------------------------------------------------------------------
+// Every rank's [rows][hidden] bf16 partial sum lives at the same offset of a buffer that is bound to one NVLink
+// multicast object; `mc` is the multicast address of that buffer.  A rank owns 1/world of the 16-byte pieces: for each
+// it issues multimem.ld_reduce (the switch fetches the piece from every GPU, adds in fp32, returns one bf16x2 x 4) and
+// multimem.st (the switch stores the result into every GPU's copy).  Per GPU and direction ~(1 + 1/world) x the tensor
+// crosses NVLink, against 2 (world-1)/world for a ring, and the sum is rounded once.
+// Two rendezvous per call, block b of a rank with block b of every other rank: before the reads (every rank's producer
+// kernel has finished: stream order on each rank + this flag exchange) and after the stores (every rank's pieces have
+// been written everywhere).  A flag is a 32-bit epoch in the RECEIVER's memory with one writer, (block, sender); epochs
+// come from a per-block counter in local memory that the kernel advances itself, so a captured graph replays correctly.
+// Waits are bounded (about two seconds of clock64); a wait that runs out records (site << 8) | 1 in the status word and
+// the kernel carries on to its end, so the counter stays in step with the other ranks.
+constexpr int MM_BLOCKS = PYC_B200_TP_MULTIMEM_BLOCKS, MM_THREADS = 512, MM_UNROLL = 4;
+
+struct MultimemArgs {
+    char* mc;                                   // multicast address of the [rows][hidden] bf16 buffer
+    uint32_t* flags[PYC_B200_TP_MAX_RANKS];     // [MM_BLOCKS][PYC_B200_TP_MAX_RANKS] of every rank (own and peer-mapped)
+    uint32_t* epochs;                           // [MM_BLOCKS], local
+    int* status;
+    int world, rank;
+    size_t vec_begin, vec_end;                  // this rank's 16-byte pieces
+};
+
+__device__ __forceinline__ void mm_rendezvous(const MultimemArgs& a, uint32_t epoch, int site) {
+    __syncthreads();
+    const int peer = threadIdx.x;
+    if (peer < a.world && peer != a.rank) {
+        __threadfence_system();
+        uint32_t* theirs = a.flags[peer] + blockIdx.x * PYC_B200_TP_MAX_RANKS + a.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+        const uint32_t* mine = a.flags[a.rank] + blockIdx.x * PYC_B200_TP_MAX_RANKS + peer;
+        const long long t0 = clock64();
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (static_cast<int32_t>(v - epoch) >= 0) break;
+            if (clock64() - t0 > 4000000000ll) { atomicCAS(a.status, 0, (site << 8) | 1); break; }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(MM_THREADS) tp_allreduce_multimem_kernel(MultimemArgs a) {
+    const uint32_t epoch = a.epochs[blockIdx.x];
+    mm_rendezvous(a, epoch + 1, 40);
+    const size_t stride = static_cast<size_t>(gridDim.x) * MM_THREADS;
+    for (size_t i0 = a.vec_begin + blockIdx.x * static_cast<size_t>(MM_THREADS) + threadIdx.x; i0 < a.vec_end; i0 += stride * MM_UNROLL) {
+        uint32_t v[MM_UNROLL][4];
+#pragma unroll
+        for (int u = 0; u < MM_UNROLL; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i < a.vec_end)
+                asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3]) : "l"(a.mc + i * 16) : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < MM_UNROLL; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i < a.vec_end)
+                asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                             ::"l"(a.mc + i * 16), "r"(v[u][0]), "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3]) : "memory");
+        }
+    }
+    mm_rendezvous(a, epoch + 2, 41);
+    if (threadIdx.x == 0) a.epochs[blockIdx.x] = epoch + 2;
+}
+
 }  // namespace
 }  // namespace b200
 
 extern "C" {
+
+int pyc_b200_tp_allreduce_multimem(void* multicast_ptr, void* const* flag_ptrs, void* epoch_counters, int world, int rank,
+                                   size_t rows, size_t hidden, void* stream) {
+    using namespace b200;
+    if (!multicast_ptr || !flag_ptrs || !epoch_counters || world < 2 || world > PYC_B200_TP_MAX_RANKS || rank < 0 || rank >= world || rows == 0 || hidden == 0) {
+        set_error("tp multimem all-reduce: bad arguments"); return -1;
+    }
+    if (hidden % 8 != 0 || reinterpret_cast<uintptr_t>(multicast_ptr) % 16) { set_error("tp multimem all-reduce: hidden must be a multiple of 8 and the buffer 16-byte aligned"); return -1; }
+    MultimemArgs a;
+    a.mc = static_cast<char*>(multicast_ptr);
+    for (int i = 0; i < PYC_B200_TP_MAX_RANKS; ++i) {
+        a.flags[i] = i < world ? static_cast<uint32_t*>(flag_ptrs[i]) : nullptr;
+        if (i < world && !flag_ptrs[i]) { set_error("tp multimem all-reduce: flag buffer %d is NULL", i); return -1; }
+    }
+    a.epochs = static_cast<uint32_t*>(epoch_counters);
+    a.status = device_status_word();
+    if (!a.status) return -1;
+    a.world = world; a.rank = rank;
+    const size_t total = rows * (hidden / 8);
+    a.vec_begin = total * static_cast<size_t>(rank) / world;
+    a.vec_end = total * static_cast<size_t>(rank + 1) / world;
+    if (sm_count() < MM_BLOCKS) { set_error("tp multimem all-reduce: needs %d co-resident blocks, the device has %d SMs", MM_BLOCKS, sm_count()); return -1; }
+    tp_allreduce_multimem_kernel<<<MM_BLOCKS, MM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    B200_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return 0;
+}
 
 int pyc_b200_tp_reduce_broadcast(const void* recv_local, void* const* outs, int world, int rank, int rows_per_rank, int hidden, void* stream) {
     using namespace b200;

@@ -102,8 +102,8 @@ class FfnBlock:
 
     def __init__(self, tokens, hidden, inner_local, w1, s1, w2, s2, torch, group=None, exchange="nccl", comm=None, single=False):
         self.torch, self.group = torch, group
-        if exchange not in ("nccl", "peer"):
-            raise ValueError("exchange must be 'nccl' or 'peer'")
+        if exchange not in ("nccl", "peer", "multimem"):
+            raise ValueError("exchange must be 'nccl', 'peer' or 'multimem'")
         self.tokens, self.hidden, self.inner = tokens, hidden, inner_local
         dev = "cuda"
         self.w1 = torch.from_numpy(np.ascontiguousarray(w1)).to(dev)
@@ -118,8 +118,10 @@ class FfnBlock:
         self.ws_bytes = backend.ffn_workspace_bytes(tokens, hidden, inner_local)
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
         self.out = torch.zeros((tokens, hidden), dtype=torch.bfloat16, device=dev)
-        self.comm, self._own_comm, self.peer = comm, False, None
-        if self.parallel and self.comm is None:
+        self.comm, self._own_comm, self.peer, self.switch = comm, False, None, None
+        if exchange == "multimem" and self.parallel:
+            self.switch = MultimemExchange(tokens, hidden, torch, group)      # needs no communicator
+        elif self.parallel and self.comm is None:
             self.comm, self._own_comm = CollectiveBackend(torch, group), True
         if exchange == "peer" and self.parallel:
             self.peer = PeerExchange(tokens, hidden, torch, self.comm, group)
@@ -136,6 +138,12 @@ class FfnBlock:
             backend.tp_reduce_broadcast(px.recv_ptrs[px.rank], px.out_ptrs, px.rank, px.rows, self.hidden, stream=s)
             self.comm.barrier(s)    # every rank has written its rows into this rank's output
             return px.out
+        if self.switch is not None:
+            sw = self.switch
+            backend.ffn_block(self.tokens, self.hidden, self.inner, x_dev.data_ptr(), self.w1.data_ptr(), self.s1.data_ptr(),
+                              self.w2.data_ptr(), self.s2.data_ptr(), sw.out.data_ptr(), self.ws.data_ptr(), self.ws_bytes, stream=s)
+            backend.tp_allreduce_multimem(sw.multicast_ptr, sw.flag_ptrs, sw.epochs.data_ptr(), sw.rank, self.tokens, self.hidden, stream=s)
+            return sw.out
         backend.ffn_block_tp(self.tokens, self.hidden, self.inner, x_dev.data_ptr(), self.w1.data_ptr(), self.s1.data_ptr(),
                              self.w2.data_ptr(), self.s2.data_ptr(), self.out.data_ptr(), self.ws.data_ptr(), self.ws_bytes,
                              self.comm.vtable if self.comm else None, self.comm.handle if self.comm else None, self.world, self.rank, stream=s)
@@ -167,6 +175,8 @@ class FfnBlock:
         self._graph = None
         if self.peer is not None:
             self.peer.close(); self.peer = None
+        if self.switch is not None:
+            self.switch.close(); self.switch = None
         if self._own_comm and self.comm is not None:
             self.comm.close(); self.comm = None
 
@@ -176,6 +186,41 @@ class _DeviceView:
 
     def __init__(self, ptr, shape, typestr):
         self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 3, "strides": None}
+
+
+class MultimemExchange:
+    """The [T][H] bf16 output of every rank bound to one NVLink multicast object, plus the flag words of the in-switch
+    all-reduce kernel.  torch.distributed._symmetric_memory allocates, exchanges the handles and binds the multicast
+    object; the data path is this package's kernel (multimem.ld_reduce / multimem.st on the multicast address)."""
+
+    def __init__(self, tokens, hidden, torch, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        dist = torch.distributed
+        self.torch, self.group = torch, group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > backend.TP_MAX_RANKS:
+            raise ValueError(f"{self.world} ranks: at most {backend.TP_MAX_RANKS}")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.out = symm_mem.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
+        handle = symm_mem.rendezvous(self.out, self.group)
+        self.multicast_ptr = int(getattr(handle, "multicast_ptr", 0) or 0)
+        if not self.multicast_ptr:
+            raise backend.BackendError("no NVLink multicast address for the symmetric buffer (NVSwitch multicast is not available here)")
+        self.flags = symm_mem.empty(backend.TP_MULTIMEM_BLOCKS * backend.TP_MAX_RANKS, dtype=torch.int32, device=dev)
+        self.flags.zero_()
+        flag_handle = symm_mem.rendezvous(self.flags, self.group)
+        self.flag_ptrs = [int(p) for p in flag_handle.buffer_ptrs]
+        self.epochs = torch.zeros(backend.TP_MULTIMEM_BLOCKS, dtype=torch.int32, device=dev)
+        self._handles = (handle, flag_handle)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)      # every rank's flag words are zero before anyone signals
+
+    def close(self):
+        # leave together and idle: no rank frees memory bound to the multicast object while another may still touch it
+        self.torch.cuda.synchronize()
+        self.torch.distributed.barrier(group=self.group)
+        self._handles = None
+        self.out = self.flags = self.epochs = None
 
 
 class PeerExchange:
