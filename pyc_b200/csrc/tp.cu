@@ -2,6 +2,7 @@
 // all-gather folded in (the reduced rows are stored into every rank's output over NVLink), and the CUDA-IPC helpers
 // that make a buffer writable by the other processes of the node.  No kernel here waits on another GPU.
 #include <cuda_bf16.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "internal.h"
@@ -54,7 +55,7 @@ __global__ void __launch_bounds__(256) tp_reduce_broadcast_kernel(ReduceArgs a) 
 // come from a per-block counter in local memory that the kernel advances itself, so a captured graph replays correctly.
 // Waits are bounded (about two seconds of clock64); a wait that runs out records (site << 8) | 1 in the status word and
 // the kernel carries on to its end, so the counter stays in step with the other ranks.
-constexpr int MM_BLOCKS = PYC_B200_TP_MULTIMEM_BLOCKS, MM_THREADS = 512, MM_UNROLL = 4;
+constexpr int MM_BLOCKS = PYC_B200_TP_MULTIMEM_BLOCKS, MM_MAX_THREADS = 1024;
 
 struct MultimemArgs {
     char* mc;                                   // multicast address of the [rows][hidden] bf16 buffer
@@ -84,11 +85,12 @@ __device__ __forceinline__ void mm_rendezvous(const MultimemArgs& a, uint32_t ep
     __syncthreads();
 }
 
-__global__ void __launch_bounds__(MM_THREADS) tp_allreduce_multimem_kernel(MultimemArgs a) {
+template <int MM_UNROLL>
+__global__ void __launch_bounds__(MM_MAX_THREADS) tp_allreduce_multimem_kernel(MultimemArgs a) {
     const uint32_t epoch = a.epochs[blockIdx.x];
     mm_rendezvous(a, epoch + 1, 40);
-    const size_t stride = static_cast<size_t>(gridDim.x) * MM_THREADS;
-    for (size_t i0 = a.vec_begin + blockIdx.x * static_cast<size_t>(MM_THREADS) + threadIdx.x; i0 < a.vec_end; i0 += stride * MM_UNROLL) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i0 = a.vec_begin + blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i0 < a.vec_end; i0 += stride * MM_UNROLL) {
         uint32_t v[MM_UNROLL][4];
 #pragma unroll
         for (int u = 0; u < MM_UNROLL; ++u) {
@@ -135,7 +137,12 @@ int pyc_b200_tp_allreduce_multimem(void* multicast_ptr, void* const* flag_ptrs, 
     a.vec_begin = total * static_cast<size_t>(rank) / world;
     a.vec_end = total * static_cast<size_t>(rank + 1) / world;
     if (sm_count() < MM_BLOCKS) { set_error("tp multimem all-reduce: needs %d co-resident blocks, the device has %d SMs", MM_BLOCKS, sm_count()); return -1; }
-    tp_allreduce_multimem_kernel<<<MM_BLOCKS, MM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    int threads = 128, unroll = 2;   // measured on 4 GPUs, 64 MB: 0.170 ms; 512 x 4: 0.182; 1024 x 8: 0.200 (the switch, not the latency, is the limit)
+    if (const char* e = getenv("PYC_B200_TP_MULTIMEM_THREADS")) { const int v = atoi(e); if (v >= 32 && v <= MM_MAX_THREADS && v % 32 == 0) threads = v; }
+    if (const char* e = getenv("PYC_B200_TP_MULTIMEM_UNROLL")) unroll = atoi(e);
+    if (unroll == 8) tp_allreduce_multimem_kernel<8><<<MM_BLOCKS, threads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    else if (unroll == 4) tp_allreduce_multimem_kernel<4><<<MM_BLOCKS, threads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    else tp_allreduce_multimem_kernel<2><<<MM_BLOCKS, threads, 0, static_cast<cudaStream_t>(stream)>>>(a);
     B200_CUDA_OK(cudaGetLastError());
     count_launch();
     return 0;
