@@ -81,6 +81,19 @@ def test_null_arguments_are_errors(clean_env):
     assert trace.reason == b"" and trace.cuda_requested == 0
 
 
+def test_in_switch_all_reduce_rejects_bad_arguments_before_touching_a_device(clean_env):
+    lib = backend.load()
+    flags = (C.c_void_p * 2)(0x1000, 0x2000)
+    call = lambda mc, fl, ep, world, rank, rows, hidden: lib.pyc_b200_tp_allreduce_multimem(mc, fl, ep, world, rank, rows, hidden, None)
+    assert call(None, flags, 0x3000, 2, 0, 8, 64) == -1                      # no multicast address
+    assert call(0x4000, flags, 0x3000, 1, 0, 8, 64) == -1                    # one rank has nothing to exchange
+    assert call(0x4000, flags, 0x3000, 9, 0, 8, 64) == -1                    # more than PYC_B200_TP_MAX_RANKS
+    assert call(0x4000, flags, 0x3000, 2, 2, 8, 64) == -1                    # rank out of range
+    assert call(0x4000, flags, 0x3000, 2, 0, 8, 60) == -1                    # hidden not a multiple of 8 (16-byte pieces)
+    assert call(0x4008, flags, 0x3000, 2, 0, 8, 64) == -1                    # misaligned tensor
+    assert b"multimem" in lib.pyc_b200_last_error()
+
+
 def test_forced_error(clean_env):
     clean_env["PYC_CUDA_FORCE_ERROR"] = "1"
     mod, ins, out = _kat()
