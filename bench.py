@@ -470,15 +470,15 @@ class Extras:
             comm = ffn.CollectiveBackend(torch)
             w1r, s1r, w2r = ffn.shard_weights(w1h, s1h, w2h, rank, world)
             tp = {}
-            exchanges = ["nccl", "peer", "multimem"]
+            exchanges = ["nccl", "peer", "multimem", "fused"]
             for exchange in list(exchanges):
                 try:
                     blk = ffn.FfnBlock(tokens, hidden, inner // world, w1r, s1r, w2r, s2h, torch, exchange=exchange, comm=comm)
                     built = 1
                 except Exception as exc:          # no NVLink multicast on this machine: every rank sees the same
-                    if exchange != "multimem":
+                    if exchange not in ("multimem", "fused"):
                         raise
-                    built, tp["multimem"] = 0, {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+                    built, tp[exchange] = 0, {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
                 flag = torch.tensor([built], dtype=torch.int32, device="cuda")
                 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
                 if int(flag[0]) == 0:

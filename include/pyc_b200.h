@@ -271,6 +271,25 @@ int pyc_b200_tp_reduce_broadcast(const void* recv_local, void* const* outs, int 
 #define PYC_B200_TP_MULTIMEM_BLOCKS 128
 int pyc_b200_tp_allreduce_multimem(void* multicast_ptr, void* const* flag_ptrs, void* epoch_counters, int world, int rank,
                                    size_t rows, size_t hidden, void* stream);
+/* The tensor-parallel FFN block with the all-reduce fused into its last GEMM: the fourth form of the exchange, and the one
+ * where the transfer overlaps the GEMM tile by tile.  args->out must be this rank's copy of a [tokens][hidden] bf16 buffer
+ * bound to an NVLink multicast object and `multicast_out` that buffer's multicast address (as for
+ * pyc_b200_tp_allreduce_multimem).  In the last GEMM (CTA-pair kernel) a publisher warp per CTA announces every 128 x 256
+ * part of the partial sum once it is stored (one system-scope fence, one epoch word per rank) and a reducer warp, walking
+ * the same tile order, reduces this rank's 128 / world rows of each part in the switch (multimem.ld_reduce, fp32
+ * accumulation, one rounding) and writes the sums into every rank's copy (multimem.st) while the tensor cores work on the
+ * following tiles; when the call's kernels have finished on a rank, its `out` holds the all-reduced result.  No
+ * communicator, no caller barrier.
+ *   flag_ptrs[r] : rank r's flag words, (tokens/256) * (hidden/256) * 2 * PYC_B200_TP_MAX_RANKS uint32, zeroed once, writable
+ *                  from every rank;   fin_ptrs[r] : likewise, PYC_B200_TP_FUSED_EPOCH_SLOTS * PYC_B200_TP_MAX_RANKS uint32;
+ *   epoch_counters : PYC_B200_TP_FUSED_EPOCH_SLOTS uint32 of local memory, zeroed once (the kernel advances them: the call
+ *                  can be captured in a CUDA graph and replayed).
+ * tokens and hidden multiples of 256, world 2, 4 or 8, every rank makes the same sequence of calls.  Waits are bounded
+ * (~2 s; sites 0x39-0x3c in pyc_b200_device_status()).  PyC has no counterpart. */
+#define PYC_B200_TP_FUSED_EPOCH_SLOTS 256
+int pyc_b200_ffn_block_switch_reduce(const pyc_b200_ffn_args* args, void* workspace, size_t workspace_bytes, void* multicast_out,
+                                     void* const* flag_ptrs, void* const* fin_ptrs, void* epoch_counters, int world, int rank,
+                                     void* stream);
 /* Device memory that other processes on the same node can map: allocate + export a 64-byte handle, open a peer's handle,
  * close it again, free the own allocation.  (cudaMalloc + CUDA IPC; the handle is sent by whatever channel the caller has.) */
 int pyc_b200_symm_alloc(size_t bytes, void** ptr, unsigned char handle[64]);

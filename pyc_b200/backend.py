@@ -21,7 +21,7 @@ EXPORTS = [
     # additive
     "pyc_b200_gemm", "pyc_b200_gemm_static", "pyc_b200_gemm_static_status", "pyc_b200_add", "pyc_b200_bias_act", "pyc_b200_layernorm", "pyc_b200_softmax",
     "pyc_b200_reduce_sum", "pyc_b200_quantize_rows", "pyc_b200_layernorm_quantize", "pyc_b200_gemm_fp8",
-    "pyc_b200_ffn_workspace_bytes", "pyc_b200_ffn_block", "pyc_b200_ffn_block_tp", "pyc_b200_ffn_phase_events", "pyc_b200_ffn_block_scatter", "pyc_b200_tp_reduce_broadcast", "pyc_b200_tp_allreduce_multimem",
+    "pyc_b200_ffn_workspace_bytes", "pyc_b200_ffn_block", "pyc_b200_ffn_block_tp", "pyc_b200_ffn_phase_events", "pyc_b200_ffn_block_scatter", "pyc_b200_tp_reduce_broadcast", "pyc_b200_tp_allreduce_multimem", "pyc_b200_ffn_block_switch_reduce",
     "pyc_b200_symm_alloc", "pyc_b200_symm_open", "pyc_b200_symm_close", "pyc_b200_symm_free", "pyc_b200_attention", "pyc_b200_conv2d", "pyc_b200_autotune_gemm", "pyc_b200_autotune_db_load", "pyc_b200_last_plan", "pyc_b200_plan_arena",
     "pyc_b200_get_runtime_info", "pyc_b200_set_stream", "pyc_b200_device_status", "pyc_b200_selftest_wait_timeout", "pyc_b200_last_error",
     "pyc_b200_shutdown",
@@ -73,6 +73,7 @@ def load():
     L.pyc_b200_last_plan.argtypes = [C.POINTER(abi.IrModule), C.c_char_p, sz]
     L.pyc_b200_ffn_block_scatter.argtypes = [C.POINTER(abi.FfnArgs), vp, sz, C.POINTER(vp), i, i, vp]
     L.pyc_b200_tp_reduce_broadcast.argtypes = [vp, C.POINTER(vp), i, i, i, i, vp]
+    L.pyc_b200_ffn_block_switch_reduce.argtypes = [C.POINTER(abi.FfnArgs), vp, sz, vp, C.POINTER(vp), C.POINTER(vp), vp, i, i, vp]
     L.pyc_b200_tp_allreduce_multimem.argtypes = [vp, C.POINTER(vp), vp, i, i, sz, sz, vp]
     L.pyc_b200_symm_alloc.argtypes = [sz, C.POINTER(vp), C.c_char_p]
     L.pyc_b200_symm_open.argtypes = [C.c_char_p, C.POINTER(vp)]
@@ -270,6 +271,20 @@ def tp_reduce_broadcast(recv_local, outs, rank, rows_per_rank, hidden, stream=0)
 
 
 TP_MULTIMEM_BLOCKS, TP_MAX_RANKS = 128, 8     # PYC_B200_TP_MULTIMEM_BLOCKS, PYC_B200_TP_MAX_RANKS
+
+
+TP_FUSED_EPOCH_SLOTS = 256     # PYC_B200_TP_FUSED_EPOCH_SLOTS
+
+
+def ffn_block_switch_reduce(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, out, workspace, workspace_bytes, multicast_out,
+                            flag_ptrs, fin_ptrs, epoch_counters, rank, ln_gamma=None, ln_beta=None, b1=None, b2=None, eps=1e-5, stream=0):
+    """The FFN block whose last GEMM all-reduces its result inside the NVSwitch while it runs (out: this rank's copy of the
+    multicast-bound buffer, multicast_out: its multicast address)."""
+    a = _ffn_args(tokens, hidden, inner, x, w1, w1_scale, w2, w2_scale, out, ln_gamma, ln_beta, b1, b2, eps)
+    world = len(flag_ptrs)
+    _check(load().pyc_b200_ffn_block_switch_reduce(C.byref(a), workspace, workspace_bytes, multicast_out, (C.c_void_p * world)(*flag_ptrs),
+                                                   (C.c_void_p * world)(*fin_ptrs), epoch_counters, world, rank, stream),
+           "pyc_b200_ffn_block_switch_reduce")
 
 
 def tp_allreduce_multimem(multicast_ptr, flag_ptrs, epoch_counters, rank, rows, hidden, stream=0):

@@ -15,6 +15,8 @@
 #include <cuda_fp8.h>
 #include <stdlib.h>
 
+#include <algorithm>
+
 #include "internal.h"
 #include "math.cuh"
 #include "ptx_sm100.cuh"
@@ -39,6 +41,13 @@ struct Fp8Epilogue {
     // rank (its own memory or a peer's, mapped into this process); D is unused then.
     __nv_bfloat16* dst[PYC_B200_TP_MAX_RANKS];
     int world, rows_per_rank, src_rank;
+    // In-switch all-reduce fused into the CTA-pair kernel (sw_world > 0): D is this rank's copy of a buffer bound to an
+    // NVLink multicast object, sw_mc its multicast address.
+    char* sw_mc;
+    uint32_t* sw_flags[PYC_B200_TP_MAX_RANKS];
+    uint32_t* sw_fin[PYC_B200_TP_MAX_RANKS];
+    uint32_t* sw_epochs;
+    int sw_world, sw_rank;
 };
 
 __device__ __forceinline__ void fp8_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -337,8 +346,58 @@ __device__ __forceinline__ void fp8_pair_tile_coords(int tile, int tiles_m, int 
     tn = local / gm;
 }
 
-template <int STAGES, bool B_KMAJOR>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+// ---- all-reduce of D inside the NVSwitch, fused into the pair kernel ---------------------------------------------------
+// Tensor-parallel use: every rank computes a partial sum of the SAME [M][N] result (its slice of K) into its own copy of a
+// buffer bound to one NVLink multicast object.  The unit of exchange is a CTA's part of a tile, 128 rows x 256 columns,
+// slot = tile * 2 + cta.  Two extra warps per CTA do the exchange; the epilogue warps only count themselves on a
+// shared-memory barrier after their stores, so the accumulators are released as fast as without it.
+//   publisher warp: all eight epilogue warps have stored the unit -> one system-scope fence -> one 32-bit epoch per rank
+//                   into flags[rank][slot][me] (single writer per word);
+//   reducer warp:   same tile order; when all ranks have published the unit it reduces this rank's 128 / world rows with
+//                   multimem.ld_reduce (the switch fetches the rows from every rank and adds them in fp32) and writes the
+//                   sums into every rank's copy with multimem.st, eight 512-byte rows in flight.
+// The exchange of tile i thus runs while the tensor cores work on tiles i+1, i+2, ...  At the end every reducer warp
+// meets the reducer warps of the same CTA index on the other ranks (fin flags): when the kernel has finished on a rank,
+// every rank's sums have landed in its D.  All waits are bounded and report through the status word.
+// Measured with the fence in the epilogue warps instead: each fence stalls its warp ~8 us, the epilogue falls behind
+// the tensor cores and the GEMM takes 0.23 ms instead of 0.09 (4 GPUs, 8192 x 4096 x 4096).
+// Needs M % 256 == 0, N % 256 == 0, world in {2, 4, 8}.
+__device__ __forceinline__ bool sw_poll(const Fp8Epilogue& ep, const uint32_t* words, uint32_t epoch) {
+    const int lane = threadIdx.x & 31;
+    bool ok = true;
+    if (lane < ep.sw_world) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(words + lane) : "memory");
+        ok = static_cast<int32_t>(v - epoch) >= 0;
+    }
+    return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ bool sw_wait(const Fp8Epilogue& ep, const uint32_t* words, uint32_t epoch, int* status, int site) {
+    const long long t0 = clock64();
+    while (!sw_poll(ep, words, epoch)) {
+        if (clock64() - t0 > 4000000000ll) { if ((threadIdx.x & 31) == 0) atomicCAS(status, ST_OK, (site << 8) | 1); return false; }
+    }
+    return true;
+}
+// every lane's earlier global stores -> visible at system scope, then the epoch into word [slot][me] of every rank
+__device__ __forceinline__ void sw_publish(const Fp8Epilogue& ep, uint32_t* const* table, size_t slot, uint32_t epoch) {
+    const int lane = threadIdx.x & 31;
+    __syncwarp();
+    if (lane < ep.sw_world) {
+        __threadfence_system();
+        uint32_t* w = table[lane] + slot * PYC_B200_TP_MAX_RANKS + ep.sw_rank;
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(w), "r"(epoch) : "memory");
+    }
+}
+__device__ __forceinline__ void sw_ld_reduce(char* addr, uint32_t (&v)[4]) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "l"(addr) : "memory");
+}
+__device__ __forceinline__ void sw_st(char* addr, const uint32_t (&v)[4]) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+}
+template <int STAGES, bool B_KMAJOR, bool SWITCH_REDUCE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SWITCH_REDUCE ? PAIR_THREADS + 64 : PAIR_THREADS, 1)
 gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Fp8Epilogue ep, int M, int N, int K, int* status) {
     constexpr uint32_t PAIR_TX = 2 * (A_STAGE_BYTES + PB_STAGE_BYTES);
     constexpr uint32_t TMEM_COLS = 2 * PBN;
@@ -350,8 +409,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
     uint8_t* sOut = sB + STAGES * PB_STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + PAIR_EPI_WARPS * 4096);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 6);
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16, stored0 = tempty0 + 16;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
@@ -365,6 +424,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         prefetch_tmap(&tmB);
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 2 * PAIR_EPI_WARPS); }  // epilogue warps of both CTAs
+        for (int a = 0; a < 2; ++a) mbar_init(stored0 + 8 * a, PAIR_EPI_WARPS);   // this CTA's epilogue warps have stored their part of a tile
         fence_barrier_init();
         fence_proxy_async();
     }
@@ -431,7 +491,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 }
             }
         }
-    } else {
+    } else if (warp < 2 + PAIR_EPI_WARPS) {
         // Eight epilogue warps: two per TMEM lane quarter, each taking half of the tile's columns.  With fp8 the main loop of a
         // tile is half as long as with bf16 while the epilogue (dequantise, bias, GELU, pack) is the same work, so four warps
         // could not keep up at K = 4096.
@@ -453,14 +513,56 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                                        vec_ok, sOut + (warp - 2) * 4096);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * acc);
+            if (lane == 0) {
+                if (SWITCH_REDUCE) mbar_arrive(stored0 + 8 * acc);   // before the accumulator goes back: a warp is never two tiles ahead of this count
+                mbar_arrive_cluster(tempty_leader0 + 8 * acc);
+            }
         }
+    } else if (SWITCH_REDUCE && warp == 2 + PAIR_EPI_WARPS) {
+        // Publisher warp: when this CTA's eight epilogue warps have stored their parts of a tile, ONE system-scope fence
+        // (it costs ~8 us here, which is why no epilogue warp executes it) and one epoch word per rank.
+        const uint32_t sw_epoch = ep.sw_epochs[blockIdx.x] + 1;
+        int it = 0;
+        for (int tile = pair; tile < num_tiles; tile += pairs, ++it) {
+            if (!mbar_wait(stored0 + 8 * (it & 1), (it >> 1) & 1, status, 0x39)) break;
+            if (lane < ep.sw_world) {
+                __threadfence_system();
+                uint32_t* w = ep.sw_flags[lane] + static_cast<size_t>(tile * 2 + static_cast<int>(rank)) * PYC_B200_TP_MAX_RANKS + ep.sw_rank;
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(w), "r"(sw_epoch) : "memory");
+            }
+            __syncwarp();
+        }
+    } else if (SWITCH_REDUCE && warp == 3 + PAIR_EPI_WARPS) {
+        // Reducer warp: follows the same tile order, waits until all ranks have published their 128 x 256 part and reduces
+        // this rank's 128 / world rows of it in the switch, one 512-byte row per instruction, eight rows in flight.
+        const uint32_t sw_epoch = ep.sw_epochs[blockIdx.x] + 1;
+        const int share = 2 * BM / 2 / ep.sw_world;          // rows of a CTA's 128 that this rank reduces
+        bool ok = true;
+        for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
+            int tm, tn;
+            fp8_pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            ok = sw_wait(ep, ep.sw_flags[ep.sw_rank] + static_cast<size_t>(tile * 2 + static_cast<int>(rank)) * PYC_B200_TP_MAX_RANKS, sw_epoch, status, 0x3a);
+            if (!ok) break;
+            char* base = ep.sw_mc + (static_cast<size_t>(tm * 2 * BM + static_cast<int>(rank) * BM + ep.sw_rank * share) * N + tn * PBN + lane * 8) * 2;
+            const size_t row_bytes = static_cast<size_t>(N) * 2;
+            for (int j0 = 0; j0 < share; j0 += 8) {      // eight rows (4 KB) in flight; sixteen were slower (0.219 against 0.197 ms at 4 GPUs)
+                uint32_t v[8][4];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sw_ld_reduce(base + (j0 + j) * row_bytes, v[j]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sw_st(base + (j0 + j) * row_bytes, v[j]);
+            }
+        }
+        // this rank's sums have been written everywhere; leave only when the reducer warps of all ranks say the same
+        sw_publish(ep, ep.sw_fin, static_cast<size_t>(blockIdx.x), sw_epoch);
+        sw_wait(ep, ep.sw_fin[ep.sw_rank] + static_cast<size_t>(blockIdx.x) * PYC_B200_TP_MAX_RANKS, sw_epoch, status, 0x3c);
     }
 
     // Both CTAs meet here (also after a timed-out wait): neither exits while the other may still signal its barriers
     // or read its shared memory.
     tc_fence_before();
     cluster_sync_all();
+    if (SWITCH_REDUCE && threadIdx.x == 0) ep.sw_epochs[blockIdx.x] += 1;   // every epilogue thread read it before the loop
     if (warp == 1) {
         if (*reinterpret_cast<volatile int*>(status) != ST_OK) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
         tc_fence_after();
@@ -468,10 +570,10 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
 }
 
-template <int STAGES, bool B_KMAJOR>
+template <int STAGES, bool B_KMAJOR, bool SWITCH_REDUCE = false>
 int launch_fp8_pair_instance(int M, int N, int K, const void* A, const void* B, const Fp8Epilogue& ep, cudaStream_t stream, int* status) {
-    auto kernel = gemm_fp8_pair_kernel<STAGES, B_KMAJOR>;
-    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + PB_STAGE_BYTES) + PAIR_EPI_WARPS * 4096 + (2 * STAGES + 4) * 8 + 16;
+    auto kernel = gemm_fp8_pair_kernel<STAGES, B_KMAJOR, SWITCH_REDUCE>;
+    constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + PB_STAGE_BYTES) + PAIR_EPI_WARPS * 4096 + (2 * STAGES + 6) * 8 + 16;
     static bool attr_set[16] = {};
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
@@ -486,7 +588,7 @@ int launch_fp8_pair_instance(int M, int N, int K, const void* A, const void* B, 
     const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + PBN - 1) / PBN);
     const int max_pairs = sm_count() / 2;
     const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
-    kernel<<<grid, PAIR_THREADS, smem, stream>>>(tmA, tmB, ep, M, N, K, status);
+    kernel<<<grid, SWITCH_REDUCE ? PAIR_THREADS + 64 : PAIR_THREADS, smem, stream>>>(tmA, tmB, ep, M, N, K, status);
     B200_CUDA_OK(cudaGetLastError());
     count_launch();
     return 0;
@@ -495,7 +597,7 @@ int launch_fp8_pair_instance(int M, int N, int K, const void* A, const void* B, 
 }  // namespace
 
 int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col_major, const float* row_scale, const float* col_scale,
-                    const void* bias, int act, void* D, cudaStream_t stream, int* status, const Fp8Scatter* scatter) {
+                    const void* bias, int act, void* D, cudaStream_t stream, int* status, const Fp8Scatter* scatter, const Fp8SwitchReduce* sw) {
     if (M <= 0 || N <= 0 || K <= 0 || !A || !B || (!D && !scatter) || !status) { set_error("fp8 gemm: bad shape or NULL pointer"); return -1; }
     if (scatter && (scatter->world < 1 || scatter->world > PYC_B200_TP_MAX_RANKS || scatter->rank < 0 || scatter->rank >= scatter->world ||
                     M % scatter->world != 0)) { set_error("fp8 gemm: bad scatter description (world %d, rank %d, M %d)", scatter->world, scatter->rank, M); return -1; }
@@ -507,6 +609,25 @@ int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col
     ep.bias = static_cast<const __nv_bfloat16*>(bias); ep.act = act;
     ep.world = 0; ep.rows_per_rank = 0; ep.src_rank = 0;
     for (int i = 0; i < PYC_B200_TP_MAX_RANKS; ++i) ep.dst[i] = nullptr;
+    ep.sw_mc = nullptr; ep.sw_epochs = nullptr; ep.sw_world = 0; ep.sw_rank = 0;
+    for (int i = 0; i < PYC_B200_TP_MAX_RANKS; ++i) { ep.sw_flags[i] = nullptr; ep.sw_fin[i] = nullptr; }
+    if (sw) {
+        const int w = sw->world;
+        if (scatter || b_col_major || !D || (w != 2 && w != 4 && w != 8) || sw->rank < 0 || sw->rank >= w || M % 256 || N % 256 || !sw->multicast_d || !sw->epochs ||
+            reinterpret_cast<uintptr_t>(sw->multicast_d) % 16 || reinterpret_cast<uintptr_t>(D) % 16) {
+            set_error("fp8 gemm with in-switch reduce: needs row-major B, M %% 256 == 0, N %% 256 == 0, 2, 4 or 8 ranks, a 16-byte aligned D and its multicast address");
+            return -1;
+        }
+        if (2 * std::min(static_cast<long long>(M / 256) * (N / 256), static_cast<long long>(sm_count() / 2)) > PYC_B200_TP_FUSED_EPOCH_SLOTS) {
+            set_error("fp8 gemm with in-switch reduce: more CTAs than PYC_B200_TP_FUSED_EPOCH_SLOTS"); return -1;
+        }
+        ep.sw_mc = static_cast<char*>(sw->multicast_d); ep.sw_epochs = static_cast<uint32_t*>(sw->epochs); ep.sw_world = w; ep.sw_rank = sw->rank;
+        for (int i = 0; i < w; ++i) {
+            if (!sw->flags[i] || !sw->fin[i]) { set_error("fp8 gemm with in-switch reduce: flag buffer %d is NULL", i); return -1; }
+            ep.sw_flags[i] = static_cast<uint32_t*>(sw->flags[i]); ep.sw_fin[i] = static_cast<uint32_t*>(sw->fin[i]);
+        }
+        return launch_fp8_pair_instance<6, false, true>(M, N, K, A, B, ep, stream, status);
+    }
     if (scatter) {
         ep.world = scatter->world; ep.rows_per_rank = M / scatter->world; ep.src_rank = scatter->rank;
         for (int i = 0; i < scatter->world; ++i) {

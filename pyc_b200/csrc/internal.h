@@ -115,8 +115,17 @@ struct Fp8Scatter {
     void* dst[PYC_B200_TP_MAX_RANKS];   // receive buffer of every rank: [world][M / world][N] bf16
     int world, rank;
 };
+// In-switch all-reduce of D fused into the GEMM (CTA-pair kernel only): see gemm_fp8.cu.
+struct Fp8SwitchReduce {
+    void* multicast_d;                       // multicast address of D (every rank's D bound to one NVLink multicast object)
+    void* flags[PYC_B200_TP_MAX_RANKS];      // per rank: [(M/256) * (N/256) * 2][PYC_B200_TP_MAX_RANKS] uint32
+    void* fin[PYC_B200_TP_MAX_RANKS];        // per rank: [PYC_B200_TP_FUSED_EPOCH_SLOTS][PYC_B200_TP_MAX_RANKS] uint32
+    void* epochs;                            // local: [PYC_B200_TP_FUSED_EPOCH_SLOTS] uint32
+    int world, rank;
+};
 int launch_gemm_fp8(int M, int N, int K, const void* A, const void* B, int b_col_major, const float* row_scale, const float* col_scale,
-                    const void* bias, int act, void* D, cudaStream_t stream, int* status, const Fp8Scatter* scatter = nullptr);
+                    const void* bias, int act, void* D, cudaStream_t stream, int* status, const Fp8Scatter* scatter = nullptr,
+                    const Fp8SwitchReduce* switch_reduce = nullptr);
 
 // ---- registry -------------------------------------------------------------------
 void registry_init_once();

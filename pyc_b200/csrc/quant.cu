@@ -231,7 +231,8 @@ static inline void ffn_mark(int i, cudaStream_t s) {
     if (g_ffn_phase_events && g_ffn_phase_events[i]) cudaEventRecord(static_cast<cudaEvent_t>(g_ffn_phase_events[i]), s);
 }
 
-static int ffn_block_impl(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* stream, const b200::Fp8Scatter* scatter) {
+static int ffn_block_impl(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* stream, const b200::Fp8Scatter* scatter,
+                          const b200::Fp8SwitchReduce* switch_reduce = nullptr) {
     if (!a || !a->x || !a->w1 || !a->w2 || !a->w1_scale || !a->w2_scale || (!a->out && !scatter) || !workspace) { set_error("ffn: NULL argument"); return -1; }
     const size_t need = pyc_b200_ffn_workspace_bytes(a->tokens, a->hidden, a->inner);
     if (need == 0 || workspace_bytes < need) { set_error("ffn: workspace of %zu bytes needed, %zu given", need, workspace_bytes); return -1; }
@@ -256,7 +257,7 @@ static int ffn_block_impl(const pyc_b200_ffn_args* a, void* workspace, size_t wo
     ffn_mark(2, s);
     if (launch_rowquant<false>(h, nullptr, nullptr, hq, hs, T, I, 0.0f, s) != 0) return -1;
     ffn_mark(3, s);
-    if (launch_gemm_fp8(a->tokens, a->hidden, a->inner, hq, a->w2, 0, hs, a->w2_scale, a->b2, PYC_B200_ACT_NONE, a->out, s, st, scatter) != 0) return -1;
+    if (launch_gemm_fp8(a->tokens, a->hidden, a->inner, hq, a->w2, 0, hs, a->w2_scale, a->b2, PYC_B200_ACT_NONE, a->out, s, st, scatter, switch_reduce) != 0) return -1;
     ffn_mark(4, s);
     return 0;
 }
@@ -285,6 +286,17 @@ int pyc_b200_ffn_block_tp(const pyc_b200_ffn_args* a, const pyc_collective_comm*
         return -1;
     }
     return 0;
+}
+
+int pyc_b200_ffn_block_switch_reduce(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* multicast_out,
+                                     void* const* flag_ptrs, void* const* fin_ptrs, void* epoch_counters, int world, int rank, void* stream) {
+    if (!a || !multicast_out || !flag_ptrs || !fin_ptrs || !epoch_counters || world < 2 || world > PYC_B200_TP_MAX_RANKS || rank < 0 || rank >= world) {
+        set_error("ffn switch reduce: bad world/rank or NULL argument"); return -1;
+    }
+    b200::Fp8SwitchReduce sw;
+    sw.multicast_d = multicast_out; sw.epochs = epoch_counters; sw.world = world; sw.rank = rank;
+    for (int i = 0; i < PYC_B200_TP_MAX_RANKS; ++i) { sw.flags[i] = i < world ? flag_ptrs[i] : nullptr; sw.fin[i] = i < world ? fin_ptrs[i] : nullptr; }
+    return ffn_block_impl(a, workspace, workspace_bytes, stream, nullptr, &sw);
 }
 
 int pyc_b200_ffn_block_scatter(const pyc_b200_ffn_args* a, void* workspace, size_t workspace_bytes, void* const* recv_slots, int world, int rank,

@@ -102,8 +102,8 @@ class FfnBlock:
 
     def __init__(self, tokens, hidden, inner_local, w1, s1, w2, s2, torch, group=None, exchange="nccl", comm=None, single=False):
         self.torch, self.group = torch, group
-        if exchange not in ("nccl", "peer", "multimem"):
-            raise ValueError("exchange must be 'nccl', 'peer' or 'multimem'")
+        if exchange not in ("nccl", "peer", "multimem", "fused"):
+            raise ValueError("exchange must be 'nccl', 'peer', 'multimem' or 'fused'")
         self.tokens, self.hidden, self.inner = tokens, hidden, inner_local
         dev = "cuda"
         self.w1 = torch.from_numpy(np.ascontiguousarray(w1)).to(dev)
@@ -119,8 +119,9 @@ class FfnBlock:
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
         self.out = torch.zeros((tokens, hidden), dtype=torch.bfloat16, device=dev)
         self.comm, self._own_comm, self.peer, self.switch = comm, False, None, None
-        if exchange == "multimem" and self.parallel:
-            self.switch = MultimemExchange(tokens, hidden, torch, group)      # needs no communicator
+        self.fused = exchange == "fused" and self.parallel
+        if exchange in ("multimem", "fused") and self.parallel:
+            self.switch = MultimemExchange(tokens, hidden, torch, group, fused=self.fused)      # needs no communicator
         elif self.parallel and self.comm is None:
             self.comm, self._own_comm = CollectiveBackend(torch, group), True
         if exchange == "peer" and self.parallel:
@@ -138,6 +139,12 @@ class FfnBlock:
             backend.tp_reduce_broadcast(px.recv_ptrs[px.rank], px.out_ptrs, px.rank, px.rows, self.hidden, stream=s)
             self.comm.barrier(s)    # every rank has written its rows into this rank's output
             return px.out
+        if self.switch is not None and self.fused:
+            sw = self.switch
+            backend.ffn_block_switch_reduce(self.tokens, self.hidden, self.inner, x_dev.data_ptr(), self.w1.data_ptr(), self.s1.data_ptr(),
+                                            self.w2.data_ptr(), self.s2.data_ptr(), sw.out.data_ptr(), self.ws.data_ptr(), self.ws_bytes,
+                                            sw.multicast_ptr, sw.unit_flag_ptrs, sw.fin_ptrs, sw.fused_epochs.data_ptr(), sw.rank, stream=s)
+            return sw.out
         if self.switch is not None:
             sw = self.switch
             backend.ffn_block(self.tokens, self.hidden, self.inner, x_dev.data_ptr(), self.w1.data_ptr(), self.s1.data_ptr(),
@@ -193,7 +200,7 @@ class MultimemExchange:
     all-reduce kernel.  torch.distributed._symmetric_memory allocates, exchanges the handles and binds the multicast
     object; the data path is this package's kernel (multimem.ld_reduce / multimem.st on the multicast address)."""
 
-    def __init__(self, tokens, hidden, torch, group=None):
+    def __init__(self, tokens, hidden, torch, group=None, fused=False):
         import torch.distributed._symmetric_memory as symm_mem
         dist = torch.distributed
         self.torch, self.group = torch, group if group is not None else dist.group.WORLD
@@ -211,7 +218,20 @@ class MultimemExchange:
         flag_handle = symm_mem.rendezvous(self.flags, self.group)
         self.flag_ptrs = [int(p) for p in flag_handle.buffer_ptrs]
         self.epochs = torch.zeros(backend.TP_MULTIMEM_BLOCKS, dtype=torch.int32, device=dev)
-        self._handles = (handle, flag_handle)
+        self._handles = [handle, flag_handle]
+        if fused:      # per-piece flags and end-of-kernel flags of the GEMM with the reduction in its epilogue
+            if tokens % 256 or hidden % 256:
+                raise ValueError("the fused exchange needs tokens and hidden to be multiples of 256")
+            units = (tokens // 256) * (hidden // 256) * 2      # one per CTA and tile of the pair kernel
+            self.unit_flags = symm_mem.empty(units * backend.TP_MAX_RANKS, dtype=torch.int32, device=dev)
+            self.unit_flags.zero_()
+            h1 = symm_mem.rendezvous(self.unit_flags, self.group)
+            self.fin = symm_mem.empty(backend.TP_FUSED_EPOCH_SLOTS * backend.TP_MAX_RANKS, dtype=torch.int32, device=dev)
+            self.fin.zero_()
+            h2 = symm_mem.rendezvous(self.fin, self.group)
+            self.unit_flag_ptrs, self.fin_ptrs = [int(p) for p in h1.buffer_ptrs], [int(p) for p in h2.buffer_ptrs]
+            self.fused_epochs = torch.zeros(backend.TP_FUSED_EPOCH_SLOTS, dtype=torch.int32, device=dev)
+            self._handles += [h1, h2]
         torch.cuda.synchronize()
         dist.barrier(group=group)      # every rank's flag words are zero before anyone signals
 
@@ -221,6 +241,7 @@ class MultimemExchange:
         self.torch.distributed.barrier(group=self.group)
         self._handles = None
         self.out = self.flags = self.epochs = None
+        self.unit_flags = self.fin = self.fused_epochs = None
 
 
 class PeerExchange:

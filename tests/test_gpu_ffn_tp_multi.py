@@ -1,6 +1,7 @@
 """GPU, one process per GPU: the tensor-parallel FFN block (benchmark configuration 5's partitioning) across real ranks.
-The three exchanges -- the all-reduce through PyC's collective vtable served by this package's NCCL backend, the exchange
-by stores into peer memory, and the in-switch all-reduce on an NVLink multicast address -- are compared with the CPU oracle's unsharded block on sampled rows (fp8 tolerance 6e-2).
+The four exchanges -- the all-reduce through PyC's collective vtable served by this package's NCCL backend, the exchange
+by stores into peer memory, the in-switch all-reduce on an NVLink multicast address, and the GEMM with that reduction fused
+into its epilogue -- are compared with the CPU oracle's unsharded block on sampled rows (fp8 tolerance 6e-2).
 Skipped on a machine with one GPU; there the kernels are covered by the one-GPU emulation in test_gpu_ffn_fp8.py and the
 vtable call by test_gpu_ffn_vtable.py."""
 import os
@@ -27,5 +28,6 @@ def test_all_exchanges_match_the_oracle_on_two_gpus():
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     lines = re.findall(r"tp_worker rank (\d)/2 exchange (\w+): max_rel_err_vs_oracle ([0-9.e+-]+)", r.stdout)
-    assert sorted((int(k), e) for k, e, _ in lines) == [(r_, e) for r_ in (0, 1) for e in ("multimem", "nccl", "peer")], r.stdout[-2000:]
+    assert sorted((int(k), e) for k, e, _ in lines) == [(r_, e) for r_ in (0, 1) for e in ("fused", "multimem", "nccl", "peer")], r.stdout[-2000:]
     assert all(float(v) <= 6e-2 for _, _, v in lines)
+    assert r.stdout.count("fused == multimem in every element: True") == 2, r.stdout[-2000:]

@@ -1,6 +1,7 @@
 """Worker for the multi-GPU tensor-parallel FFN test: one process per GPU (torchrun), benchmark configuration 5's block
-with the inner dimension sharded over the ranks.  All three exchanges run -- the all-reduce through PyC's collective vtable
-(NCCL backend), the peer-store exchange and the in-switch (multimem) all-reduce -- and EACH result is compared with the CPU oracle's unsharded block on sampled
+with the inner dimension sharded over the ranks.  All four exchanges run -- the all-reduce through PyC's collective vtable
+(NCCL backend), the peer-store exchange, the in-switch (multimem) all-reduce and the GEMM with that reduction fused into its
+epilogue -- and EACH result is compared with the CPU oracle's unsharded block on sampled
 token rows (fp8 tolerance 6e-2, norm-wise).  Prints one line per rank and exchange that the test parses.
 
     python -m torch.distributed.run --nproc-per-node 2 ... tests/tp_worker.py --tokens 1024 --hidden 1024 --inner 4096
@@ -24,7 +25,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=1024); ap.add_argument("--hidden", type=int, default=1024); ap.add_argument("--inner", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=48, help="token rows compared with the oracle")
-    ap.add_argument("--exchanges", default="nccl,peer,multimem")
+    ap.add_argument("--exchanges", default="nccl,peer,multimem,fused")
     a = ap.parse_args()
     world, rank, local = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -40,13 +41,14 @@ def main():
     X = torch.from_numpy(xb.view(np.int16)).cuda()
     comm = ffn.CollectiveBackend(torch)
     ok = True
+    full = {}
     for exchange in a.exchanges.split(","):
         blk = ffn.FfnBlock(a.tokens, a.hidden, a.inner // world, w1r, s1r, w2r, s2, torch, exchange=exchange, comm=comm)
         for _ in range(3):                     # repeated calls: the in-switch exchange advances its epoch counters each time
             out = blk.run(X)
         torch.cuda.synchronize()
         status = backend.device_status()
-        if exchange == "multimem" and status == 0:   # ...and a captured graph replays with the counters it finds
+        if exchange in ("multimem", "fused") and status == 0:   # ...and a captured graph replays with the counters it finds
             replay = blk.capture(X)
             for _ in range(2):
                 out = replay()
@@ -55,6 +57,12 @@ def main():
         if status != 0:                        # no assert here: every rank leaves through the orderly shutdown below
             print(f"tp_worker rank {rank}/{world} exchange {exchange}: device status {status:#x}", flush=True)
             ok = False
+        full[exchange] = out.clone()
+        if exchange == "fused" and "multimem" in full:
+            # the same partial sums reduced by the same switch operation: the two results must agree in every element
+            same = bool(torch.equal(full["fused"].view(torch.int16), full["multimem"].view(torch.int16)))
+            print(f"tp_worker rank {rank}/{world} fused == multimem in every element: {same}", flush=True)
+            ok = ok and same
         got = out[rows].float().cpu().numpy()
         err = float(np.abs(got - want).max() / np.abs(want).max())
         print(f"tp_worker rank {rank}/{world} exchange {exchange}: max_rel_err_vs_oracle {err:.4e} rows {len(rows)}", flush=True)
