@@ -43,7 +43,19 @@ def main():
     ok = True
     full = {}
     for exchange in a.exchanges.split(","):
-        blk = ffn.FfnBlock(a.tokens, a.hidden, a.inner // world, w1r, s1r, w2r, s2, torch, exchange=exchange, comm=comm)
+        try:
+            blk, why = ffn.FfnBlock(a.tokens, a.hidden, a.inner // world, w1r, s1r, w2r, s2, torch, exchange=exchange, comm=comm), ""
+        except Exception as exc:                  # a machine without NVLink multicast has no in-switch exchanges
+            if exchange not in ("multimem", "fused"):
+                raise
+            blk, why = None, f"{type(exc).__name__}: {exc}"
+        have = torch.tensor([1 if blk is not None else 0], dtype=torch.int32, device="cuda")
+        dist.all_reduce(have, op=dist.ReduceOp.MIN)
+        if int(have[0]) == 0:                     # every rank skips it together
+            if blk is not None:
+                blk.close()
+            print(f"tp_worker rank {rank}/{world} exchange {exchange}: unavailable ({why[:120]})", flush=True)
+            continue
         for _ in range(3):                     # repeated calls: the in-switch exchange advances its epoch counters each time
             out = blk.run(X)
         torch.cuda.synchronize()
