@@ -601,7 +601,8 @@ def run_only(args):
         m, n, k = dims or [8192, 8192, 2048]
         a = torch.randint(0, 120, (m, k), dtype=torch.uint8, device="cuda", generator=g); b = torch.randint(0, 120, (k, n), dtype=torch.uint8, device="cuda", generator=g)
         rs, cs, d = torch.ones(m, device="cuda"), torch.ones(n, device="cuda"), torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
-        run = lambda: backend.gemm_fp8(m, n, k, a.data_ptr(), b.data_ptr(), d.data_ptr(), rs.data_ptr(), cs.data_ptr(), None, abi.ACT_GELU)
+        act8 = {"none": abi.ACT_NONE, "bias_relu": abi.ACT_RELU, "bias_gelu": abi.ACT_GELU}[args.epilogue]
+        run = lambda: backend.gemm_fp8(m, n, k, a.data_ptr(), b.data_ptr(), d.data_ptr(), rs.data_ptr(), cs.data_ptr(), None, act8)
         work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
     elif args.only == "ffn":
         from pyc_b200 import ffn

@@ -309,8 +309,12 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 // Arrive on an mbarrier that may live in the other CTA (cluster address).
+// Arrive on a barrier that may live in the other CTA of the pair.  Default semantics (release at CTA scope): what is handed
+// over is a TMEM accumulator whose reads have completed (tcgen05.wait::ld + tcgen05.fence::before_thread_sync), not global
+// data.  A cluster-scope release here would first wait until the warp's global stores of the output tile are visible to
+// the other SM -- a microsecond or two per tile during which the accumulator is not given back.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 // Per-CTA tile load of a pair: data lands in THIS CTA's shared memory, the bytes are
 // counted on the barrier at `cluster_bar` (the leader's).
