@@ -1293,7 +1293,7 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
         const char* pe = getenv("PYC_B200_ATTENTION_POLY");
         const int poly = pe && pe[0] >= '0' && pe[0] <= '2' ? pe[0] - '0' : 0;
         constexpr size_t smem = AttnSmem4<HD>::BYTES > 120 * 1024 ? AttnSmem4<HD>::BYTES : 120 * 1024;   // one CTA per SM: it takes all 512 TMEM columns
-        static bool attr_set4[16][3] = {};
+        static std::atomic<bool> attr_set4[16][3];   // zero-initialised; set-once per device, a repeated set is harmless
         auto k0 = attention_tc4_kernel<HD, FMT, 0>;
         auto k1 = attention_tc4_kernel<HD, FMT, 1>;
         auto k2 = attention_tc4_kernel<HD, FMT, 2>;
@@ -1308,7 +1308,7 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
         auto kernel = attention_tc_kernel<HD, FMT>;
         // At least 120 KB so that two CTAs never share an SM: each one takes all 512 TMEM columns.
         constexpr size_t smem = AttnSmem<HD>::BYTES > 120 * 1024 ? AttnSmem<HD>::BYTES : 120 * 1024;
-        static bool attr_set[16] = {};
+        static std::atomic<bool> attr_set[16];   // zero-initialised; set-once per device, a repeated set is harmless
         if (dev < 16 && !attr_set[dev]) {
             B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
             attr_set[dev] = true;
@@ -1318,7 +1318,7 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
         const char* pe = getenv("PYC_B200_ATTENTION_POLY");
         const bool poly = pe && pe[0] == '1';
         constexpr size_t smem = AttnSmem3<HD>::BYTES > 76 * 1024 ? AttnSmem3<HD>::BYTES : 76 * 1024;   // two CTAs per SM, 256 TMEM columns each
-        static bool attr_set3[16][2] = {};
+        static std::atomic<bool> attr_set3[16][2];   // zero-initialised; set-once per device, a repeated set is harmless
         auto k_poly = attention_tc3_kernel<HD, FMT, true>;
         auto k_mufu = attention_tc3_kernel<HD, FMT, false>;
         if (dev < 16 && !attr_set3[dev][poly]) {
@@ -1343,7 +1343,7 @@ int launch_attention_tc(pyc_dtype dt, int bh, int seq, const void* q, const void
         const bool poly = pe && pe[0] == '1';
         // Never less than 76 KB: at most two CTAs per SM, because each takes 256 of the 512 TMEM columns.
         constexpr size_t smem = AttnSmem2<HD>::BYTES > 76 * 1024 ? AttnSmem2<HD>::BYTES : 76 * 1024;
-        static bool attr_set2[16][2] = {};
+        static std::atomic<bool> attr_set2[16][2];   // zero-initialised; set-once per device, a repeated set is harmless
         auto k_poly = attention_tc2_kernel<HD, FMT, true>;
         auto k_mufu = attention_tc2_kernel<HD, FMT, false>;
         if (dev < 16 && !attr_set2[dev][poly]) {

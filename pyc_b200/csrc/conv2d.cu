@@ -17,6 +17,7 @@
 // (tcgen05.mma into TMEM, double-buffered accumulators, epilogue warps) has the
 // structure of the GEMM kernel in gemm_tc.cu.  Stride-1 convolutions with
 // C % 8 == 0 take this path; anything else runs the direct kernel below.
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdlib.h>
@@ -269,7 +270,7 @@ template <int BN, int STAGES, int FMT, int CTAS_PER_SM = 1>
 int launch_conv_tc(const CUtensorMap& tmIn, const CUtensorMap& tmW, const ConvParams& cp, cudaStream_t stream, int* status) {
     auto kernel = conv2d_tc_kernel<BN, STAGES, FMT, CTAS_PER_SM>;
     constexpr size_t smem = conv_smem_bytes<BN, STAGES>();
-    static bool attr_set[16] = {};
+    static std::atomic<bool> attr_set[16];   // zero-initialised; set-once per device, a repeated set is harmless
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 16 && !attr_set[dev]) {

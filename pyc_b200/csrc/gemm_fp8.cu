@@ -11,6 +11,7 @@
 // epilogue warps); what changes is the element size: a 128-byte swizzle row holds
 // 128 k-values, one MMA consumes K = 32, B stored [K,N] row-major is the MN-major
 // operand with 128-column slabs (LBO = 16 KB, SBO = 1 KB).
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <stdlib.h>
@@ -304,7 +305,7 @@ template <int BN, int STAGES, bool B_KMAJOR>
 int launch_fp8_instance(int M, int N, int K, const void* A, const void* B, const Fp8Epilogue& ep, cudaStream_t stream, int* status) {
     auto kernel = gemm_fp8_kernel<BN, STAGES, B_KMAJOR>;
     constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + BN * BK) + EPI_STAGE_BYTES + (2 * STAGES + 4) * 8 + 16;
-    static bool attr_set[16] = {};
+    static std::atomic<bool> attr_set[16];   // zero-initialised; set-once per device, a repeated set is harmless
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 16 && !attr_set[dev]) {
@@ -351,8 +352,8 @@ __device__ __forceinline__ void fp8_pair_tile_coords(int tile, int tiles_m, int 
 // buffer bound to one NVLink multicast object.  The unit of exchange is a CTA's part of a tile, 128 rows x 256 columns,
 // slot = tile * 2 + cta.  Two extra warps per CTA do the exchange; the epilogue warps only count themselves on a
 // shared-memory barrier after their stores, so the accumulators are released as fast as without it.
-//   publisher warp: all eight epilogue warps have stored the unit -> one system-scope fence -> one 32-bit epoch per rank
-//                   into flags[rank][slot][me] (single writer per word);
+//   publisher warp: whenever all eight epilogue warps have stored further units (a shared-memory counter) -> one
+//                   system-scope fence -> one 32-bit epoch per rank and unit into flags[rank][slot][me] (single writer per word);
 //   reducer warp:   same tile order; when all ranks have published the unit it reduces this rank's 128 / world rows with
 //                   multimem.ld_reduce (the switch fetches the rows from every rank and adds them in fp32) and writes the
 //                   sums into every rank's copy with multimem.st, eight 512-byte rows in flight.
@@ -424,7 +425,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         prefetch_tmap(&tmB);
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 2 * PAIR_EPI_WARPS); }  // epilogue warps of both CTAs
-        for (int a = 0; a < 2; ++a) mbar_init(stored0 + 8 * a, PAIR_EPI_WARPS);   // this CTA's epilogue warps have stored their part of a tile
+        *reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4) = 0u;   // at stored0: how many (epilogue warp, tile) parts this CTA has stored
         fence_barrier_init();
         fence_proxy_async();
     }
@@ -514,23 +515,38 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                if (SWITCH_REDUCE) mbar_arrive(stored0 + 8 * acc);   // before the accumulator goes back: a warp is never two tiles ahead of this count
+                if (SWITCH_REDUCE) asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(stored0) : "memory");
                 mbar_arrive_cluster(tempty_leader0 + 8 * acc);
             }
         }
     } else if (SWITCH_REDUCE && warp == 2 + PAIR_EPI_WARPS) {
-        // Publisher warp: when this CTA's eight epilogue warps have stored their parts of a tile, ONE system-scope fence
-        // (it costs ~8 us here, which is why no epilogue warp executes it) and one epoch word per rank.
+        // Publisher warp.  The epilogue warps count every part they have stored on a shared-memory counter (a counter, not
+        // a phase barrier: the publisher may fall several tiles behind, its fence costs ~8 us and a tile can be shorter).
+        // Whenever whole tiles have been stored since the last look: ONE system-scope fence, then one epoch word per rank
+        // and tile.
         const uint32_t sw_epoch = ep.sw_epochs[blockIdx.x] + 1;
-        int it = 0;
-        for (int tile = pair; tile < num_tiles; tile += pairs, ++it) {
-            if (!mbar_wait(stored0 + 8 * (it & 1), (it >> 1) & 1, status, 0x39)) break;
-            if (lane < ep.sw_world) {
-                __threadfence_system();
-                uint32_t* w = ep.sw_flags[lane] + static_cast<size_t>(tile * 2 + static_cast<int>(rank)) * PYC_B200_TP_MAX_RANKS + ep.sw_rank;
-                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(w), "r"(sw_epoch) : "memory");
+        const int my_tiles = pair < num_tiles ? (num_tiles - pair + pairs - 1) / pairs : 0;
+        int published = 0;
+        const long long t0 = clock64();
+        while (published < my_tiles) {
+            uint32_t c;
+            asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(c) : "r"(stored0) : "memory");
+            const int done = static_cast<int>(c / PAIR_EPI_WARPS);
+            if (done > published) {
+                if (lane < ep.sw_world) {
+                    __threadfence_system();
+                    for (int i = published; i < done; ++i) {
+                        const int tile = pair + i * pairs;
+                        uint32_t* w = ep.sw_flags[lane] + static_cast<size_t>(tile * 2 + static_cast<int>(rank)) * PYC_B200_TP_MAX_RANKS + ep.sw_rank;
+                        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(w), "r"(sw_epoch) : "memory");
+                    }
+                }
+                __syncwarp();
+                published = done;
+            } else if (clock64() - t0 > 4000000000ll) {
+                if (lane == 0) atomicCAS(status, ST_OK, (0x39 << 8) | 1);
+                break;
             }
-            __syncwarp();
         }
     } else if (SWITCH_REDUCE && warp == 3 + PAIR_EPI_WARPS) {
         // Reducer warp: follows the same tile order, waits until all ranks have published their 128 x 256 part and reduces
@@ -574,7 +590,7 @@ template <int STAGES, bool B_KMAJOR, bool SWITCH_REDUCE = false>
 int launch_fp8_pair_instance(int M, int N, int K, const void* A, const void* B, const Fp8Epilogue& ep, cudaStream_t stream, int* status) {
     auto kernel = gemm_fp8_pair_kernel<STAGES, B_KMAJOR, SWITCH_REDUCE>;
     constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE_BYTES + PB_STAGE_BYTES) + PAIR_EPI_WARPS * 4096 + (2 * STAGES + 6) * 8 + 16;
-    static bool attr_set[16] = {};
+    static std::atomic<bool> attr_set[16];   // zero-initialised; set-once per device, a repeated set is harmless
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 16 && !attr_set[dev]) {

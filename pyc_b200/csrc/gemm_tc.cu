@@ -20,6 +20,7 @@
 // MN-major operand: each TMA box is 64 n-values (128 B) by 64 k-rows, boxes for
 // consecutive 64-column chunks sit 8 KB apart (descriptor LBO), 8-row groups
 // 1 KB apart (SBO).  B stored [N,K] is the K-major form.
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -319,7 +320,7 @@ template <int BN, int STAGES, bool B_KMAJOR, int FMT>
 int launch_instance(const GemmProblem& p, cudaStream_t stream, int* status) {
     auto kernel = gemm_tc_kernel<BN, STAGES, B_KMAJOR, FMT>;
     constexpr size_t smem = tc_smem_bytes<BN, STAGES>();
-    static bool attr_set[16] = {};
+    static std::atomic<bool> attr_set[16];   // zero-initialised; set-once per device, a repeated set is harmless
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 16 && !attr_set[dev]) {

@@ -11,6 +11,7 @@
 //     arriving on the leader's barrier
 // No multicast of any kind is used: every CTA fetches its own operand halves.
 // Replaces the same PyC code as gemm_tc.cu (cutlass_kernels/gemm/kernel.cu:48-84).
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdlib.h>
@@ -317,7 +318,7 @@ template <int STAGES, bool B_KMAJOR, int FMT>
 int launch_pair_instance(const GemmProblem& p, cudaStream_t stream, int* status) {
     auto kernel = gemm_tc2_kernel<STAGES, B_KMAJOR, FMT>;
     constexpr size_t smem = 1024 + static_cast<size_t>(STAGES) * (A_STAGE + B_STAGE) + (STAGES <= 6 ? 8 * 4096 : 0) + (2 * STAGES + 4) * 8 + 16;
-    static bool attr_set[16] = {};
+    static std::atomic<bool> attr_set[16];   // zero-initialised; set-once per device, a repeated set is harmless
     int dev = 0;
     B200_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 16 && !attr_set[dev]) {

@@ -35,3 +35,21 @@ def test_all_exchanges_match_the_oracle_on_two_gpus():
     assert all(float(v) <= 6e-2 for _, _, v in lines)
     if not skipped:
         assert r.stdout.count("fused == multimem in every element: True") == 2, r.stdout[-2000:]
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_in_switch_exchanges_with_many_short_tiles_per_cta():
+    # inner 4096 over two ranks: K = 2048 per rank in the last GEMM, seven tiles per CTA pair of ~4 us each, shorter than the
+    # publisher warp's system-scope fence: the fused exchange must tolerate a publisher that is several tiles behind
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29543", os.path.join(ROOT, "tests", "tp_worker.py"), "--tokens", "8192", "--hidden", "4096", "--inner", "4096",
+           "--exchanges", "multimem,fused"]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    if "unavailable" in r.stdout:
+        pytest.skip("no NVLink multicast on this machine")
+    lines = re.findall(r"tp_worker rank (\d)/2 exchange (\w+): max_rel_err_vs_oracle ([0-9.e+-]+)", r.stdout)
+    assert sorted((int(k), e) for k, e, _ in lines) == [(r_, e) for r_ in (0, 1) for e in ("fused", "multimem")], r.stdout[-2000:]
+    assert all(float(v) <= 6e-2 for _, _, v in lines)
+    assert r.stdout.count("fused == multimem in every element: True") == 2, r.stdout[-2000:]
