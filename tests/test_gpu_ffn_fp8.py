@@ -46,7 +46,8 @@ def test_fp8_gemm_with_scales(backend, oracle_lib, fp8_kernel, shape, colmajor):
     assert rel_err(got, want) <= 2e-2 / 4   # output is bf16-rounded; the products themselves are exact in fp32
 
 
-@pytest.mark.parametrize("shape", [(64, 256), (37, 4096), (16, 16384), (5, 1024)])
+# rows >= 64 and 1024 / 2048 / 4096 columns take the one-warp-per-row kernels (row counts that do not fill the last CTA)
+@pytest.mark.parametrize("shape", [(64, 256), (37, 4096), (16, 16384), (5, 1024), (100, 4096), (67, 2048), (201, 1024)])
 def test_row_quantisers(backend, oracle_lib, shape):
     import torch
     from gpu_util import sync_ok
