@@ -257,6 +257,21 @@ __device__ __forceinline__ void widen(const RawVec<T, VEC>& r, float (&f)[VEC]) 
     }
 }
 
+// Running maximum over packed 16-bit pairs (exact: a maximum needs no widening); four instructions per 8 elements.
+__device__ __forceinline__ void raw_max_acc(const uint4& u, __nv_bfloat162& m) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+    m = __hmax2(m, __hmax2(__hmax2(p[0], p[1]), __hmax2(p[2], p[3])));
+}
+__device__ __forceinline__ void raw_max_acc(const uint4& u, __half2& m) {
+    const __half2* p = reinterpret_cast<const __half2*>(&u);
+    m = __hmax2(m, __hmax2(__hmax2(p[0], p[1]), __hmax2(p[2], p[3])));
+}
+__device__ __forceinline__ float pair_max(const __nv_bfloat162& m) { return fmaxf(__low2float(m), __high2float(m)); }
+__device__ __forceinline__ float pair_max(const __half2& m) { return fmaxf(__low2float(m), __high2float(m)); }
+template <typename T> struct Pair16;
+template <> struct Pair16<__nv_bfloat16> { using type = __nv_bfloat162; __device__ static type lowest() { return __floats2bfloat162_rn(-INFINITY, -INFINITY); } };
+template <> struct Pair16<__half> { using type = __half2; __device__ static type lowest() { return __floats2half2_rn(-INFINITY, -INFINITY); } };
+
 // One row per group of THREADS threads (THREADS = 32: four rows per CTA).  Each thread
 // owns up to VPT vectors of its row in registers; CACHED == false is the any-width form
 // that re-reads the row from global memory instead.
@@ -339,10 +354,18 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
             }
         } else {  // softmax
             float mx = -INFINITY;
-            for_each([&](float (&f)[VEC], size_t) {
+            if constexpr (CACHED && VEC == 8) {       // 16-bit storage: the maximum straight from the packed pairs
+                typename Pair16<T>::type m2 = Pair16<T>::lowest();
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) mx = fmaxf(mx, f[j]);
-            });
+                for (int i = 0; i < VPT; ++i)
+                    if (tid + static_cast<size_t>(i) * THREADS < nvec) raw_max_acc(raw[i].u, m2);
+                mx = pair_max(m2);
+            } else {
+                for_each([&](float (&f)[VEC], size_t) {
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) mx = fmaxf(mx, f[j]);
+                });
+            }
             mx = block_max<THREADS>(mx, scratch);
             // exp(x - max) = 2^(x*log2e - max*log2e): one FMA + one special-function op per element (arguments <= 0: the
             // flush-to-zero form needs none of exp2f's range handling; 2 ulp)
@@ -350,23 +373,42 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
             float den = 0.0f;
             if constexpr (CACHED && VPT * VEC * (sizeof(T) == 4 ? 2 : 1) <= 32) {
                 float e[NV][VEC];   // the exponentials are computed once and kept for the normalising pass (when they fit in registers)
+                unsigned long long den2 = 0ull;   // bit pattern of (0.0f, 0.0f)
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const size_t vi = tid + static_cast<size_t>(i) * THREADS;
                     if (vi < nvec) {
                         float f[VEC];
                         widen<T, VEC>(raw[i], f);
+                        if constexpr (VEC % 2 == 0) {   // exponent arguments and the running sum two elements per instruction
+                            const unsigned long long l2e2 = f32x2_splat(l2e), ms2 = f32x2_splat(mshift);
 #pragma unroll
-                        for (int j = 0; j < VEC; ++j) { e[i][j] = ex2_approx(fmaf(f[j], l2e, mshift)); den += e[i][j]; }
+                            for (int j = 0; j < VEC; j += 2) {
+                                float t0, t1;
+                                f32x2_unpack(f32x2_fma(f32x2_pack(f[j], f[j + 1]), l2e2, ms2), t0, t1);
+                                e[i][j] = ex2_approx(t0); e[i][j + 1] = ex2_approx(t1);
+                                den2 = f32x2_add(den2, f32x2_pack(e[i][j], e[i][j + 1]));
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < VEC; ++j) { e[i][j] = ex2_approx(fmaf(f[j], l2e, mshift)); den += e[i][j]; }
+                        }
                     }
                 }
+                if constexpr (VEC % 2 == 0) { float lo, hi; f32x2_unpack(den2, lo, hi); den = lo + hi; }
                 const float inv = 1.0f / block_sum<THREADS>(den, scratch);
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const size_t vi = tid + static_cast<size_t>(i) * THREADS;
                     if (vi < nvec) {
+                        if constexpr (VEC % 2 == 0) {
+                            const unsigned long long inv2 = f32x2_splat(inv);
 #pragma unroll
-                        for (int j = 0; j < VEC; ++j) e[i][j] *= inv;
+                            for (int j = 0; j < VEC; j += 2) f32x2_unpack(f32x2_mul(f32x2_pack(e[i][j], e[i][j + 1]), inv2), e[i][j], e[i][j + 1]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < VEC; ++j) e[i][j] *= inv;
+                        }
                         store_vec<T, VEC>(orow + vi * VEC, e[i]);
                     }
                 }

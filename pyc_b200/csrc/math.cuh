@@ -51,6 +51,11 @@ __device__ __forceinline__ unsigned long long f32x2_mul(unsigned long long a, un
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
+__device__ __forceinline__ unsigned long long f32x2_add(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ unsigned long long f32x2_splat(float a) { return f32x2_pack(a, a); }
 
 // gelu_erf on two values at once; same polynomial, same results as the scalar form up to the sign assembly, which is
