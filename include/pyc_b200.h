@@ -284,7 +284,8 @@ int pyc_b200_tp_allreduce_multimem(void* multicast_ptr, void* const* flag_ptrs, 
  *                  from every rank;   fin_ptrs[r] : likewise, PYC_B200_TP_FUSED_EPOCH_SLOTS * PYC_B200_TP_MAX_RANKS uint32;
  *   epoch_counters : PYC_B200_TP_FUSED_EPOCH_SLOTS uint32 of local memory, zeroed once (the kernel advances them: the call
  *                  can be captured in a CUDA graph and replayed).
- * tokens and hidden multiples of 256, world 2, 4 or 8, every rank makes the same sequence of calls.  Waits are bounded
+ * tokens and hidden multiples of 256, world 2, 4 or 8, every rank makes the same sequence of calls, and one set of flag /
+ * counter buffers serves ONE problem shape (the epochs are per CTA, the flags per tile).  Waits are bounded
  * (~2 s; sites 0x39-0x3c in pyc_b200_device_status()).  PyC has no counterpart. */
 #define PYC_B200_TP_FUSED_EPOCH_SLOTS 256
 int pyc_b200_ffn_block_switch_reduce(const pyc_b200_ffn_args* args, void* workspace, size_t workspace_bytes, void* multicast_out,
