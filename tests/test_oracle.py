@@ -169,3 +169,37 @@ def test_gelu_and_layernorm_definitions_agree_with_torch_fp64(oracle_lib):
         want_plain = torch.nn.functional.layer_norm(torch.from_numpy(x).double(), (300,), eps=1e-5).numpy()
     np.testing.assert_allclose(oracle_lib.layernorm(x, gamma, beta), want_affine, rtol=1e-5, atol=2e-6)
     np.testing.assert_allclose(oracle_lib.layernorm(x), want_plain, rtol=1e-5, atol=2e-6)
+
+
+def test_attention_conv_softmax_and_e4m3_definitions_agree_with_torch(oracle_lib):
+    """The reference holds nothing that pins attention (its kernel is an identity stub), conv2d (fp16-only CUTLASS
+    instantiation), softmax (no executor) or fp8 (no dtype).  The oracle's restated definitions are therefore also held to
+    an independent implementation: torch on the CPU in fp64 -- scaled_dot_product_attention with and without the causal
+    mask, conv2d as cross-correlation on NHWC / KRSC data with symmetric padding and a stride, softmax over the last
+    axis -- and torch's own float8_e4m3fn decoding for every one of the 256 codes."""
+    import torch
+    F = torch.nn.functional
+    q = workloads.normal((2, 3, 40, 16), 31); k = workloads.normal((2, 3, 40, 16), 32); v = workloads.normal((2, 3, 40, 16), 33)
+    scale = 1 / math.sqrt(16)
+    for causal in (False, True):
+        want = F.scaled_dot_product_attention(torch.from_numpy(q).double(), torch.from_numpy(k).double(), torch.from_numpy(v).double(),
+                                              is_causal=causal, scale=scale).numpy()
+        got = oracle_lib.attention(q.reshape(6, 40, 16), k.reshape(6, 40, 16), v.reshape(6, 40, 16), scale, causal).reshape(2, 3, 40, 16)
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+    x = workloads.uniform((2, 9, 7, 8), 41); w = workloads.uniform((5, 3, 3, 8), 42); b = workloads.uniform((5,), 43)
+    for pad, stride in (((1, 1), (1, 1)), ((0, 0), (1, 1)), ((1, 1), (2, 2)), ((2, 1), (1, 2))):
+        want = F.conv2d(torch.from_numpy(x).double().permute(0, 3, 1, 2), torch.from_numpy(w).double().permute(0, 3, 1, 2),
+                        torch.from_numpy(b).double(), stride=stride, padding=pad).permute(0, 2, 3, 1).numpy()
+        np.testing.assert_allclose(oracle_lib.conv2d(x, w, b, pad=pad, stride=stride, relu=False), want, rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(oracle_lib.conv2d(x, w, b, pad=pad, stride=stride, relu=True), np.maximum(want, 0), rtol=1e-5, atol=1e-5)
+    s = workloads.normal((11, 257), 51, 4.0)
+    np.testing.assert_allclose(oracle_lib.softmax(s), F.softmax(torch.from_numpy(s).double(), dim=-1).numpy(), rtol=1e-5, atol=1e-8)
+    codes = np.arange(256, dtype=np.uint8)
+    want = torch.from_numpy(codes).view(torch.float8_e4m3fn).float().numpy()
+    got = workloads.e4m3_decode(codes)
+    finite = np.isfinite(want)                      # 0x7f / 0xff are NaN in e4m3fn; the encoder never produces them
+    assert finite.sum() == 254
+    np.testing.assert_array_equal(got[finite], want[finite])
+    vals = workloads.normal((4096,), 61, 100.0)
+    enc = torch.from_numpy(np.clip(vals, -448.0, 448.0)).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    np.testing.assert_array_equal(workloads.e4m3_encode(vals), enc)     # round to nearest even, saturating at +-448
