@@ -203,3 +203,19 @@ def test_attention_conv_softmax_and_e4m3_definitions_agree_with_torch(oracle_lib
     vals = workloads.normal((4096,), 61, 100.0)
     enc = torch.from_numpy(np.clip(vals, -448.0, 448.0)).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
     np.testing.assert_array_equal(workloads.e4m3_encode(vals), enc)     # round to nearest even, saturating at +-448
+
+
+def test_ffn_block_definition_agrees_with_torch(oracle_lib):
+    """The FFN block the fp8 kernels are held to (LayerNorm without affine, dequantised e4m3 weights with one scale per output
+    channel, exact-erf GELU, fp32 contractions in PyC's summation order) against the same chain in torch fp64."""
+    import torch
+    import oracle
+    F = torch.nn.functional
+    tokens, hidden, inner = 24, 64, 256
+    xb, w1, s1, w2, s2 = workloads.ffn_inputs(tokens, hidden, inner)
+    x = workloads.bf16_bits_to_f32(xb)
+    got = oracle.ffn_reference(oracle_lib, x, w1, s1, w2, s2)
+    deq = lambda codes, scale: torch.from_numpy(codes).view(torch.float8_e4m3fn).double() * torch.from_numpy(np.asarray(scale)).double()[None, :]
+    h = F.gelu(F.layer_norm(torch.from_numpy(x).double(), (hidden,), eps=1e-5) @ deq(w1, s1))
+    want = (h @ deq(w2, s2)).numpy()
+    assert np.abs(got - want).max() / np.abs(want).max() <= 1e-5
