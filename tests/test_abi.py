@@ -94,6 +94,20 @@ def test_in_switch_all_reduce_rejects_bad_arguments_before_touching_a_device(cle
     assert b"multimem" in lib.pyc_b200_last_error()
 
 
+def test_fused_switch_reduce_rejects_bad_arguments_before_touching_a_device(clean_env):
+    lib = backend.load()
+    args = abi.FfnArgs()
+    ptrs = (C.c_void_p * 2)(0x1000, 0x2000)
+    call = lambda a, mc, fl, fin, ep, world, rank: lib.pyc_b200_ffn_block_switch_reduce(a, 0x5000, 1 << 20, mc, fl, fin, ep, world, rank, None)
+    assert call(None, 0x4000, ptrs, ptrs, 0x3000, 2, 0) == -1                      # no arguments
+    assert call(C.byref(args), None, ptrs, ptrs, 0x3000, 2, 0) == -1               # no multicast address
+    assert call(C.byref(args), 0x4000, None, ptrs, 0x3000, 2, 0) == -1             # no flag table
+    assert call(C.byref(args), 0x4000, ptrs, ptrs, None, 2, 0) == -1               # no epoch counters
+    assert call(C.byref(args), 0x4000, ptrs, ptrs, 0x3000, 1, 0) == -1             # one rank has nothing to exchange
+    assert call(C.byref(args), 0x4000, ptrs, ptrs, 0x3000, 2, 5) == -1             # rank out of range
+    assert b"switch reduce" in lib.pyc_b200_last_error()
+
+
 def test_forced_error(clean_env):
     clean_env["PYC_CUDA_FORCE_ERROR"] = "1"
     mod, ins, out = _kat()
